@@ -215,7 +215,16 @@ class VizosunConfig(LibraryConfig):
     architecture = "Vizosun"
 
 
-_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig, "Vokelix": VokelixConfig, "Vizosun": VizosunConfig}
+class KudonexConfig(LibraryConfig):
+    """The Kudonex decoder (`config/kudonex.h`): `layers` (a list of {type: "mlstm" | "mamba2" | "attention",
+    mixer: {...}, mlp: {kind: "moe", expert: {ff}, router: {experts, top, groups: {count, keep}}, shared: {ff}} | None}),
+    `width`, `vocab`, `norm` ({eps}), `embedding` ({scale}), optionally `canon` ({taps}) and `max_positions`.  The
+    dictionary names the class under `architecture`."""
+
+    architecture = "Kudonex"
+
+
+_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig, "Vokelix": VokelixConfig, "Vizosun": VizosunConfig, "Kudonex": KudonexConfig}
 _CALLBACKS = {}      # name -> (ctypes callback, holder of the last returned text): kept alive while registered
 
 
@@ -258,7 +267,7 @@ def register_architecture(name: str, config_cls: type, aliases=()):
 def unregister_architecture(name: str):
     _b.check(_b.lib().illm_unregister_architecture(name.encode()))
     _CALLBACKS.pop(name, None)
-    if _PY_CLASSES.get(name) not in (LlamaConfig, VokelixConfig, VizosunConfig):
+    if _PY_CLASSES.get(name) not in (LlamaConfig, VokelixConfig, VizosunConfig, KudonexConfig):
         _PY_CLASSES.pop(name, None)
 
 

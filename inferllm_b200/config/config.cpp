@@ -212,6 +212,7 @@ Registry& registry() {
 void register_llama_architecture();     // config/llama.cpp
 void register_vokelix_architecture();   // config/vokelix.cpp
 void register_vizosun_architecture();   // config/vizosun.cpp
+void register_kudonex_architecture();   // config/kudonex.cpp
 
 static void ensure_builtin() {
     static bool done = false;
@@ -220,6 +221,7 @@ static void ensure_builtin() {
         register_llama_architecture();
         register_vokelix_architecture();
         register_vizosun_architecture();
+        register_kudonex_architecture();
     }
 }
 

@@ -58,6 +58,10 @@ struct DecayScanArgs {
     int inline_prep;                // the scan prepares q, k, v itself while it stages them (steps of few tokens)
     int segments;                   // a sequence's tokens of this step in up to so many segments side by side (1: in order)
     float* seg_state;               // [B, segments, nh, dv, d]: what each segment's own tokens add to the state
+    // per-token gates (decay_scan_kernel<.., GATED>): S_t = ga[t, h] S_(t-1) + gb[t, h] k_t v_t^T in place of the fixed decay
+    const float *ga, *gb;           // [T, nh]
+    int qk_div;                     // value head h reads query/key head h / qk_div (1: a head of its own)
+    long long state_stride;         // floats from one slot's state to the next (nh * d * dv unless more is kept beside S)
 };
 
 __device__ __forceinline__ float act_of(float v, int act) {
@@ -119,7 +123,11 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 // o_t += decay^(t - t0 + 1) S_in^T q_t (no chain: the tokens are independent), and the last segment
 // writes the sequence's state.  The sums then have another order than token by token, so the float32
 // mode, which promises the same bits however a prompt is cut, never asks for segments.
-template <int R, int C, int LI, int PASS>
+//
+// GATED: the decay is not one number per head but a gate per token and head, a_t, and the token's outer product
+// enters with a second one, b_t: S_t = a_t S_(t-1) + b_t k_t v_t^T.  The two gates of a token travel with its staged
+// row.  Value head h may share the queries and keys of head h / qk_div.  Such a step always runs in order (one segment).
+template <int R, int C, int LI, int PASS, bool GATED>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a) {
     pdl_grid_sync();
     extern __shared__ __align__(16) float sm[];
@@ -127,7 +135,8 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     constexpr int JW = C * (32 / LI);               // columns per warp
     constexpr int JB = JW * (DS_THREADS / 32);      // columns per block
     constexpr int DP = R * LI;                      // rows with padding
-    constexpr int ROW = 2 * DP + JB;                // floats of one staged token: q, k, v
+    constexpr int ROW = 2 * DP + JB + (GATED ? 4 : 0);      // floats of one staged token: q, k, v (and the two gates)
+    constexpr int GATE_AT = 2 * DP + JB;
     const int P = a.segments;
     const int b = blockIdx.x / P, seg = blockIdx.x % P, h = blockIdx.y, j0 = blockIdx.z * JB;
     const int d = a.d, dv = a.dv;
@@ -140,8 +149,9 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     const int g = lane % LI;
     const int jl = (warp * (32 / LI) + lane / LI) * C;      // first of this thread's columns within the block
     const int jn = dv - j0 < JB ? dv - j0 : JB;     // columns of this block that exist
-    const float dec = a.decay[h];
-    float* Sg = a.state + ((size_t)a.slots[b] * a.nh + h) * (size_t)d * dv;       // [dv][d]
+    const float dec = GATED ? 1.f : a.decay[h];
+    const int hq = h / a.qk_div;                    // the head whose queries and keys this head reads
+    float* Sg = a.state + (size_t)a.slots[b] * a.state_stride + (size_t)h * d * dv;       // [dv][d]
     // row of register (m, r): m * 4 LI + 4 g + r, so that the LI lanes of a column group read 16-byte
     // pieces of q, k and the state that lie side by side
     float s[C][M][4];
@@ -229,7 +239,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
                 if (c < 2 * d) {
                     const bool is_k = c >= d;
                     const int e = is_k ? c - d : c;
-                    const float* src = row + (is_k ? a.k_off : a.q_off) + h * d;
+                    const float* src = row + (is_k ? a.k_off : a.q_off) + hq * d;
                     float val = act_of(src[e], a.qk_act);
                     if (e < a.rot) {
                         int p = a.token_pos[tb + tt];
@@ -254,8 +264,8 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
                 const int tt = idx / per, c = idx - tt * per;
                 const float* row = a.x + (size_t)(tb + tt) * a.ld;
                 float* dst = base + tt * ROW;
-                if (c < cq) cp_async16(dst + 4 * c, row + a.q_off + h * d + 4 * c);
-                else if (c < 2 * cq) cp_async16(dst + DP + 4 * (c - cq), row + a.k_off + h * d + 4 * (c - cq));
+                if (c < cq) cp_async16(dst + 4 * c, row + a.q_off + hq * d + 4 * c);
+                else if (c < 2 * cq) cp_async16(dst + DP + 4 * (c - cq), row + a.k_off + hq * d + 4 * (c - cq));
                 else cp_async16(dst + 2 * DP + 4 * (c - 2 * cq), row + a.v_off + h * dv + j0 + 4 * (c - 2 * cq));
             }
         } else {
@@ -264,11 +274,16 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
                 const int tt = idx / per, c = idx - tt * per;
                 const float* row = a.x + (size_t)(tb + tt) * a.ld;
                 float* dst = base + tt * ROW;
-                if (c < d) dst[c] = row[a.q_off + h * d + c];
-                else if (c < 2 * d) dst[DP + c - d] = row[a.k_off + h * d + c - d];
+                if (c < d) dst[c] = row[a.q_off + hq * d + c];
+                else if (c < 2 * d) dst[DP + c - d] = row[a.k_off + hq * d + c - d];
                 else dst[2 * DP + c - 2 * d] = row[a.v_off + h * dv + j0 + c - 2 * d];
             }
         }
+        if (GATED)
+            for (int tt = threadIdx.x; tt < n; tt += DS_THREADS) {
+                base[tt * ROW + GATE_AT] = a.ga[(size_t)(tb + tt) * a.nh + h];
+                base[tt * ROW + GATE_AT + 1] = a.gb[(size_t)(tb + tt) * a.nh + h];
+            }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     auto tokens = [&](auto group, const float* rowp, int t) {
@@ -280,9 +295,11 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
             const float4* k4 = reinterpret_cast<const float4*>(rowp + u * ROW + DP) + g;
             const float* vp = rowp + u * ROW + 2 * DP + jl;
             float v[C];
+            const float dec_t = GATED ? rowp[u * ROW + GATE_AT] : dec;
+            const float put_t = GATED ? rowp[u * ROW + GATE_AT + 1] : 1.f;
 #pragma unroll
             for (int c = 0; c < C; c++) {
-                v[c] = vp[c];
+                v[c] = GATED ? vp[c] * put_t : vp[c];
                 p[u][c] = 0.f;
             }
 #pragma unroll
@@ -291,10 +308,10 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
 #pragma unroll
                 for (int c = 0; c < C; c++) {
                     if (PASS == 0) {
-                        s[c][m][0] = fmaf(dec, s[c][m][0], kk.x * v[c]);
-                        s[c][m][1] = fmaf(dec, s[c][m][1], kk.y * v[c]);
-                        s[c][m][2] = fmaf(dec, s[c][m][2], kk.z * v[c]);
-                        s[c][m][3] = fmaf(dec, s[c][m][3], kk.w * v[c]);
+                        s[c][m][0] = fmaf(dec_t, s[c][m][0], kk.x * v[c]);
+                        s[c][m][1] = fmaf(dec_t, s[c][m][1], kk.y * v[c]);
+                        s[c][m][2] = fmaf(dec_t, s[c][m][2], kk.z * v[c]);
+                        s[c][m][3] = fmaf(dec_t, s[c][m][3], kk.w * v[c]);
                     }
                     p[u][c] = fmaf(s[c][m][0], qq.x, p[u][c]);
                     p[u][c] = fmaf(s[c][m][1], qq.y, p[u][c]);
@@ -378,19 +395,35 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
 // head sizes up to 1024 (the rows of a column group over at most 32 lanes), any value size
 extern "C" int illm_decay_scan_supported(int d, int dv) { return d > 0 && d <= 1024 && dv > 0 ? 1 : 0; }
 
-template <int R, int C, int LI>
+template <int R, int C, int LI, bool GATED>
 static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {
-    constexpr int DP = R * LI, JB = C * (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB;
+    constexpr int DP = R * LI, JB = C * (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB + (GATED ? 4 : 0);
     int tile = (int)(48 * 1024 / sizeof(float) / (2 * ROW));
     a.tile = tile > DS_MAX_TILE ? DS_MAX_TILE : (tile < 1 ? 1 : tile);
     const size_t smem = (size_t)2 * a.tile * ROW * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 0, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (!GATED) cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
     const dim3 grid(B * a.segments, a.nh, (a.dv + JB - 1) / JB);
-    illm_launch(decay_scan_kernel<R, C, LI, 0>, grid, dim3(DS_THREADS), smem, s, a);
-    if (a.segments > 1) illm_launch(decay_scan_kernel<R, C, LI, 1>, grid, dim3(DS_THREADS), smem, s, a);
+    illm_launch(decay_scan_kernel<R, C, LI, 0, GATED>, grid, dim3(DS_THREADS), smem, s, a);
+    if (!GATED && a.segments > 1) illm_launch(decay_scan_kernel<R, C, LI, 1, false>, grid, dim3(DS_THREADS), smem, s, a);
+}
+
+template <bool GATED>
+static void decay_launch_for(DecayScanArgs a, int B, cudaStream_t s) {
+    const int d = a.d;
+    // 16 rows x 4 columns per thread (64 state elements in registers), the rows of a column group over d / 16 lanes:
+    // a token costs a thread four 16-byte reads of q and of k, few enough to be on their way a token ahead,
+    // and the lanes few shuffles.  (Measured against 4 x 4 over 32 lanes, 16 x 8 over 8 and 64 x 2 over 2 at
+    // head size 128.)
+    if (d <= 16) decay_launch<16, 4, 1, GATED>(a, B, s);
+    else if (d <= 32) decay_launch<16, 4, 2, GATED>(a, B, s);
+    else if (d <= 64) decay_launch<16, 4, 4, GATED>(a, B, s);
+    else if (d <= 128) decay_launch<16, 4, 8, GATED>(a, B, s);
+    else if (d <= 256) decay_launch<16, 4, 16, GATED>(a, B, s);
+    else if (d <= 512) decay_launch<16, 4, 32, GATED>(a, B, s);
+    else decay_launch<32, 2, 32, GATED>(a, B, s);
 }
 
 // x: the packed projection; its q, k and v columns are prepared in place (T rows).
@@ -402,62 +435,106 @@ extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, in
     if (segments < 1 || (segments > 1 && !seg_state) || (long long)B * segments > 0x7fffffff) return ILLM_ERR_BAD_ARG;
     if (nh <= 0 || d <= 0 || d > 1024 || dv <= 0 || nh > 65535 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !state || !out)
         return ILLM_ERR_BAD_ARG;
-    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0, 0, segments, seg_state};
+    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0, 0, segments, seg_state,
+                    nullptr, nullptr, 1, (long long)nh * d * dv};
     a.vec = !((d | dv | ld | q_off | k_off | v_off) & 3) && !((uintptr_t)x & 15) && !((uintptr_t)state & 15);
     cudaStream_t s = (cudaStream_t)stream;
     // a step of few tokens (single tokens of a batch) is not worth a launch of its own for the preparation
     a.inline_prep = T <= 64 ? 1 : 0;
     if (!a.inline_prep && (qk_act || v_act || rot || k_scale != 1.0f)) illm_launch(decay_prep_kernel, dim3(T, nh), dim3(128), 0, s, a);
-    // 16 rows x 4 columns per thread (64 state elements in registers), the rows of a column group over d / 16 lanes:
-    // a token costs a thread four 16-byte reads of q and of k, few enough to be on their way a token ahead,
-    // and the lanes few shuffles.  (Measured against 4 x 4 over 32 lanes, 16 x 8 over 8 and 64 x 2 over 2 at
-    // head size 128.)
-    if (d <= 16) decay_launch<16, 4, 1>(a, B, s);
-    else if (d <= 32) decay_launch<16, 4, 2>(a, B, s);
-    else if (d <= 64) decay_launch<16, 4, 4>(a, B, s);
-    else if (d <= 128) decay_launch<16, 4, 8>(a, B, s);
-    else if (d <= 256) decay_launch<16, 4, 16>(a, B, s);
-    else if (d <= 512) decay_launch<16, 4, 32>(a, B, s);
-    else decay_launch<32, 2, 32>(a, B, s);
+    decay_launch_for<false>(a, B, s);
     return illm_launch_status();
 }
 
-// y[t, g, :] = o[t, g, :] / sqrt(mean_g(o^2) + eps) (* w) * act(gate[t, g, :]);  one block per (token, group);
-// w covers the whole row or, shorter, repeats along it
+// The same recurrence with a gate pair per token and head (ga, gb: float32 [T, nh]) in place of the fixed decay, the
+// q and k columns read as they are (nqk = nh / qk_div query/key heads).  state: the slots' S [nh, dv, d] blocks,
+// `state_stride` floats apart.
+extern "C" int illm_gated_scan(const float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int qk_div, int d, int dv, const float* ga,
+                               const float* gb, float* state, long long state_stride, const int* slots, const int* cu_q, float* out, int B,
+                               void* stream) {
+    if (B <= 0 || T <= 0) return 0;
+    if (nh <= 0 || qk_div <= 0 || nh % qk_div || d <= 0 || d > 1024 || dv <= 0 || nh > 65535 || !x || !state || !out || !ga || !gb ||
+        state_stride < (long long)nh * d * dv)
+        return ILLM_ERR_BAD_ARG;
+    DecayScanArgs a{const_cast<float*>(x), ld, q_off, k_off, v_off, nh, d, dv, 0, 0, nullptr, 0, 0, 1.f, nullptr, state, slots, cu_q, nullptr, out, nullptr,
+                    0, 0, 0, 1, nullptr, ga, gb, qk_div, state_stride};
+    a.vec = !((d | dv | ld | q_off | k_off | v_off) & 3) && !((uintptr_t)x & 15) && !((uintptr_t)state & 15) && !(state_stride & 3);
+    a.inline_prep = 0;
+    decay_launch_for<true>(a, B, (cudaStream_t)stream);
+    return illm_launch_status();
+}
+
+// y[t, g, :] = u[t, g, :] / sqrt(mean_g(u^2) + eps) (* w) * act(gate[t, g, :]);  one block per (token, group);
+// w covers the whole row or, shorter, repeats along it.  What is normed, u, is the recurrence's output o, optionally
+// times a factor per token and head (row_scale [T, width / head]), plus a skip term skip_w[head] * skip_x[t, c]
+// (skip_x: float32 rows skip_ld apart), and, with gate_first, already times the gate's activation (the gate then
+// comes before the norm instead of after it).
+struct GroupNormGateArgs {
+    const float* o;
+    int width, group;
+    const float* w;
+    int w_len;
+    float eps;
+    const float* gate;
+    int gate_ld, gate_act, gate_first;
+    const float* row_scale;
+    int head;
+    const float *skip_w, *skip_x;
+    int skip_ld;
+};
+
 template <typename TA>
-__global__ void __launch_bounds__(128)
-group_norm_gate_kernel(const float* __restrict__ o, int width, int group, const float* __restrict__ w, int w_len, float eps,
-                       const float* __restrict__ gate, int gate_ld, int gate_act, TA* __restrict__ y) {
+__global__ void __launch_bounds__(128) group_norm_gate_kernel(GroupNormGateArgs a, TA* __restrict__ y) {
     pdl_grid_sync();
     __shared__ float scratch[32];
-    const int t = blockIdx.x, g0 = blockIdx.y * group;
-    const float* row = o + (size_t)t * width + g0;
+    const int t = blockIdx.x, g0 = blockIdx.y * a.group;
+    const float* row = a.o + (size_t)t * a.width + g0;
+    const int n_heads = a.width / a.head;
+    auto value = [&](int c) {
+        float v = row[c];
+        const int h = (g0 + c) / a.head;
+        if (a.row_scale) v *= a.row_scale[(size_t)t * n_heads + h];
+        if (a.skip_w) v = fmaf(a.skip_w[h], a.skip_x[(size_t)t * a.skip_ld + g0 + c], v);
+        if (a.gate && a.gate_first) v *= act_of(a.gate[(size_t)t * a.gate_ld + g0 + c], a.gate_act);
+        return v;
+    };
     float ss = 0.f;
-    for (int c = threadIdx.x; c < group; c += blockDim.x) ss += row[c] * row[c];
+    for (int c = threadIdx.x; c < a.group; c += blockDim.x) {
+        const float v = value(c);
+        ss = fmaf(v, v, ss);
+    }
     ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)group + eps);
-    for (int c = threadIdx.x; c < group; c += blockDim.x) {
-        float v = row[c] * inv;
-        if (w) v *= w[(g0 + c) % w_len];
-        if (gate) v *= act_of(gate[(size_t)t * gate_ld + g0 + c], gate_act);
-        y[(size_t)t * width + g0 + c] = from_f32<TA>(v);
+    const float inv = 1.0f / sqrtf(ss / (float)a.group + a.eps);
+    for (int c = threadIdx.x; c < a.group; c += blockDim.x) {
+        float v = value(c) * inv;
+        if (a.w) v *= a.w[(g0 + c) % a.w_len];
+        if (a.gate && !a.gate_first) v *= act_of(a.gate[(size_t)t * a.gate_ld + g0 + c], a.gate_act);
+        y[(size_t)t * a.width + g0 + c] = from_f32<TA>(v);
     }
 }
 
-// w_len: the weight's length, the whole width or a divisor of it (a weight of one group's size is shared by the groups)
-extern "C" int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate,
-                                    int gate_ld, int gate_act, void* y, int act_dtype, void* stream) {
+// w_len: the weight's length, the whole width or a divisor of it (a weight of one group's size is shared by the groups);
+// head: columns per entry of row_scale and skip_w (0 when neither is given)
+extern "C" int illm_group_norm_gate_ex(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate,
+                                       int gate_ld, int gate_act, int gate_first, const float* row_scale, int head, const float* skip_w,
+                                       const float* skip_x, int skip_ld, void* y, int act_dtype, void* stream) {
     if (T <= 0) return 0;
     if (width <= 0 || group <= 0 || width % group || width / group > 65535 || !o || !y) return ILLM_ERR_BAD_ARG;
     if (w && (w_len <= 0 || width % w_len)) return ILLM_ERR_BAD_ARG;
+    if ((row_scale || skip_w) && (head <= 0 || width % head)) return ILLM_ERR_BAD_ARG;
+    if (skip_w && !skip_x) return ILLM_ERR_BAD_ARG;
     if (!w) w_len = width;
+    if (head <= 0) head = width;
+    GroupNormGateArgs a{o, width, group, w, w_len, eps, gate, gate_ld, gate_act, gate_first, row_scale, head, skip_w, skip_x, skip_ld};
     dim3 grid(T, width / group);
     cudaStream_t s = (cudaStream_t)stream;
-    if (act_dtype == ILLM_BF16)
-        illm_launch(group_norm_gate_kernel<bf16>, grid, dim3(128), 0, s, o, width, group, w, w_len, eps, gate, gate_ld, gate_act, (bf16*)y);
-    else if (act_dtype == ILLM_F32)
-        illm_launch(group_norm_gate_kernel<float>, grid, dim3(128), 0, s, o, width, group, w, w_len, eps, gate, gate_ld, gate_act, (float*)y);
-    else
-        return ILLM_ERR_BAD_ARG;
+    if (act_dtype == ILLM_BF16) illm_launch(group_norm_gate_kernel<bf16>, grid, dim3(128), 0, s, a, (bf16*)y);
+    else if (act_dtype == ILLM_F32) illm_launch(group_norm_gate_kernel<float>, grid, dim3(128), 0, s, a, (float*)y);
+    else return ILLM_ERR_BAD_ARG;
     return illm_launch_status();
+}
+
+extern "C" int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate,
+                                    int gate_ld, int gate_act, void* y, int act_dtype, void* stream) {
+    return illm_group_norm_gate_ex(o, T, width, group, w, w_len, eps, gate, gate_ld, gate_act, 0, nullptr, 0, nullptr, nullptr, 0, y, act_dtype, stream);
 }

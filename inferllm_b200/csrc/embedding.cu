@@ -44,6 +44,47 @@ extern "C" int illm_embedding(const int* ids, const void* table, int table_dtype
     return illm_launch_status();
 }
 
+// The same gather times a constant, plus a sinusoid position vector: entry 2i is sin(p f_i) and entry 2i + 1 is
+// cos(p f_i), f_i = base^(-2i / H) given as a float32 table [ceil(H / 2)] (made in float64 on the host); the angle
+// and the two functions are accurate float32.  inv_freq == nullptr: no position vector.
+template <typename TW>
+__global__ void embedding_scaled_kernel(const int* __restrict__ ids, const int* __restrict__ token_pos, const TW* __restrict__ table,
+                                        float* __restrict__ out, int H, int V, float scale, const float* __restrict__ inv_freq,
+                                        int* __restrict__ err) {
+    pdl_grid_sync();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * H;
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicExch(err, 1);
+        for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = 0.f;
+        return;
+    }
+    const TW* row = table + (size_t)id * H;
+    const float p = (float)token_pos[t];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = to_f32(row[c]) * scale;
+        if (inv_freq) {
+            const float ang = p * inv_freq[c >> 1];
+            v += (c & 1) ? cosf(ang) : sinf(ang);
+        }
+        o[c] = v;
+    }
+}
+
+extern "C" int illm_embedding_scaled(const int* ids, const int* token_pos, const void* table, int table_dtype, float* out, int T, int H, int V,
+                                     float scale, const float* inv_freq, int* err, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == ILLM_BF16)
+        illm_launch(embedding_scaled_kernel<bf16>, dim3(T), dim3(256), 0, s, ids, token_pos, (const bf16*)table, out, H, V, scale, inv_freq, err);
+    else if (table_dtype == ILLM_F32)
+        illm_launch(embedding_scaled_kernel<float>, dim3(T), dim3(256), 0, s, ids, token_pos, (const float*)table, out, H, V, scale, inv_freq, err);
+    else
+        return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
+}
+
 // Switches programmatic dependent launch of all kernels of the library on (1, default) or off (0).
 extern "C" int illm_set_pdl(int on) {
     g_illm_pdl = on ? 1 : 0;

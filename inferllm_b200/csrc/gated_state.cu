@@ -1,0 +1,124 @@
+// The per-token gates of two recurrences that share one form of state update,
+//
+//   S_t = a_t S_(t-1) + b_t k_t v_t^T,    o_t = S_t^T q_t          (per head; a_t, b_t scalars)
+//
+// which decay_state.cu runs with its per-token gates (decay_scan_kernel<.., GATED>).  Both kernels here turn a
+// layer's raw projections into a_t and b_t, float32 [T, heads], in accurate float32 arithmetic.
+//
+// mlstm_gates_kernel: the matrix memory with exponential gating, stabilised by a running maximum m that starts at 0:
+//   i_t = cap tanh((z_i + b_i) / cap),  f_t = logsigmoid(cap tanh((z_f + b_f) / cap))
+//   m_t = max(f_t + m_(t-1), i_t),  a_t = exp(f_t + m_(t-1) - m_t),  b_t = exp(i_t - m_t)
+//   n_t = a_t n_(t-1) + b_t k_t,  scale_t = q_scale / (max(|q_scale n_t . q_t|, exp(-m_t)) + 1e-6)
+// so that the layer's output is scale_t * S_t^T q_t with the raw q.  m and n are a chain over the sequence's tokens:
+// a warp owns one (sequence, head), keeps n over its lanes, and goes through the tokens in order; the two gates
+// (the tanh, the logarithm) are made for 32 tokens at a time, a token per lane, outside the chain.  n [heads, d] and
+// m [heads] live in the sequence's state at n_off and m_off.
+//
+// ssm_gates_kernel: the selective state space with a scalar decay per head:
+//   dt = softplus(z + dt_bias),  a_t = exp(-exp(A_log) dt),  b_t = dt
+#include "common.cuh"
+
+struct MlstmGateArgs {
+    const float* x;
+    int ld, q_off, k_off, i_off, f_off;
+    const float *i_bias, *f_bias;
+    float cap, q_scale;
+    int nh, d;
+    float* state;
+    long long state_stride, n_off, m_off;
+    const int *slots, *cu_q;
+    float *ga, *gb, *scale;
+    int B;
+};
+
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <int NR>
+__global__ void __launch_bounds__(128) mlstm_gates_kernel(MlstmGateArgs a) {
+    pdl_grid_sync();
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= a.B * a.nh) return;
+    const int b = unit / a.nh, h = unit - b * a.nh;
+    const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+    float* st = a.state + (size_t)a.slots[b] * a.state_stride;
+    float n[NR];
+#pragma unroll
+    for (int r = 0; r < NR; r++) n[r] = r * 32 + lane < a.d ? st[a.n_off + (size_t)h * a.d + r * 32 + lane] : 0.f;
+    float m = st[a.m_off + h];
+    const float bi = a.i_bias ? a.i_bias[h] : 0.f, bf = a.f_bias ? a.f_bias[h] : 0.f;
+    for (int tb = t0; tb < t1; tb += 32) {
+        const int cnt = t1 - tb < 32 ? t1 - tb : 32;
+        float ig_l = 0.f, fg_l = 0.f;
+        if (lane < cnt) {
+            const float* row = a.x + (size_t)(tb + lane) * a.ld;
+            ig_l = a.cap * tanhf((row[a.i_off + h] + bi) / a.cap);
+            fg_l = log_sigmoid_f(a.cap * tanhf((row[a.f_off + h] + bf) / a.cap));
+        }
+        for (int j = 0; j < cnt; j++) {
+            const float ig = __shfl_sync(0xffffffffu, ig_l, j), fg = __shfl_sync(0xffffffffu, fg_l, j);
+            const float* row = a.x + (size_t)(tb + j) * a.ld;
+            const float m_new = fmaxf(fg + m, ig);
+            const float ga = expf(fg + m - m_new), gb = expf(ig - m_new);
+            float dot = 0.f;
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                const int c = r * 32 + lane;
+                if (c < a.d) {
+                    n[r] = fmaf(ga, n[r], gb * row[a.k_off + h * a.d + c]);
+                    dot = fmaf(n[r], row[a.q_off + h * a.d + c], dot);
+                }
+            }
+            dot = warp_sum(dot) * a.q_scale;
+            m = m_new;
+            if (lane == 0) {
+                const size_t o = (size_t)(tb + j) * a.nh + h;
+                a.ga[o] = ga;
+                a.gb[o] = gb;
+                a.scale[o] = a.q_scale / (fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; r++)
+        if (r * 32 + lane < a.d) st[a.n_off + (size_t)h * a.d + r * 32 + lane] = n[r];
+    if (lane == 0) st[a.m_off + h] = m;
+}
+
+extern "C" int illm_mlstm_gates(const float* x, int T, int ld, int q_off, int k_off, int i_off, int f_off, const float* i_bias, const float* f_bias,
+                                float cap, float q_scale, int nh, int d, float* state, long long state_stride, long long n_off, long long m_off,
+                                const int* slots, const int* cu_q, float* ga, float* gb, float* scale, int B, void* stream) {
+    if (T <= 0 || B <= 0) return 0;
+    if (nh <= 0 || d <= 0 || d > 1024 || !(cap > 0.f) || !x || !state || !ga || !gb || !scale) return ILLM_ERR_BAD_ARG;
+    MlstmGateArgs a{x, ld, q_off, k_off, i_off, f_off, i_bias, f_bias, cap, q_scale, nh, d, state, state_stride, n_off, m_off, slots, cu_q, ga, gb, scale, B};
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(((unsigned)B * nh + 3) / 4), block(128);
+    if (d <= 32) illm_launch(mlstm_gates_kernel<1>, grid, block, 0, s, a);
+    else if (d <= 64) illm_launch(mlstm_gates_kernel<2>, grid, block, 0, s, a);
+    else if (d <= 128) illm_launch(mlstm_gates_kernel<4>, grid, block, 0, s, a);
+    else if (d <= 256) illm_launch(mlstm_gates_kernel<8>, grid, block, 0, s, a);
+    else if (d <= 512) illm_launch(mlstm_gates_kernel<16>, grid, block, 0, s, a);
+    else illm_launch(mlstm_gates_kernel<32>, grid, block, 0, s, a);
+    return illm_launch_status();
+}
+
+__global__ void ssm_gates_kernel(const float* __restrict__ x, int ld, int dt_off, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                 int nh, float* __restrict__ ga, float* __restrict__ gb, long long n) {
+    pdl_grid_sync();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / nh;
+    const int h = (int)(i - t * nh);
+    const float z = x[(size_t)t * ld + dt_off + h] + (dt_bias ? dt_bias[h] : 0.f);
+    const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+    ga[i] = expf(-expf(a_log[h]) * dt);
+    gb[i] = dt;
+}
+
+extern "C" int illm_ssm_gates(const float* x, int T, int ld, int dt_off, const float* dt_bias, const float* a_log, int nh, float* ga, float* gb,
+                              void* stream) {
+    if (T <= 0) return 0;
+    if (nh <= 0 || !x || !a_log || !ga || !gb) return ILLM_ERR_BAD_ARG;
+    const long long n = (long long)T * nh;
+    illm_launch(ssm_gates_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, x, ld, dt_off, dt_bias, a_log, nh, ga, gb, n);
+    return illm_launch_status();
+}

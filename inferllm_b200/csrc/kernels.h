@@ -26,6 +26,10 @@ int illm_attention_decode_ring_rope(const void* qkv, const float* partials, int 
 // attention_generic.cu
 int illm_attention_generic(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int page_size, int window, float scale, int dv, const float* sinks, const float* gate, int gate_stride, void* stream);
 
+// attention_mixed.cu
+int illm_attention_mixed_supported(int nh, int nkv, int d, int esize);
+int illm_attention_mixed(const void* q, int q_stride, const void* kc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int page_size, int window, float scale, const float* r1, const float* r2, const float* mix, const float* gate, int gate_stride, void* stream);
+
 // attention_prefill.cu
 int illm_attention_prefill(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, void* stream);
 
@@ -35,6 +39,8 @@ int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc
 // decay_state.cu
 int illm_decay_scan_supported(int d, int dv);
 int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act, const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots, const int* cu_q, const int* token_pos, float* out, int B, int* err, int segments, float* seg_state, void* stream);
+int illm_gated_scan(const float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int qk_div, int d, int dv, const float* ga, const float* gb, float* state, long long state_stride, const int* slots, const int* cu_q, float* out, int B, void* stream);
+int illm_group_norm_gate_ex(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate, int gate_ld, int gate_act, int gate_first, const float* row_scale, int head, const float* skip_w, const float* skip_x, int skip_ld, void* y, int act_dtype, void* stream);
 int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate, int gate_ld, int gate_act, void* y, int act_dtype, void* stream);
 
 int illm_attention_prefill_tc_ex(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, int* err, int wide_p, const float* sinks, const float* gate, int gate_stride, void* stream);
@@ -46,6 +52,16 @@ int illm_bigram_embedding(const int* ids, const int* token_pos, const int* token
 int illm_delta_rule_supported(int d, int dv, int taps);
 int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_off, int v_off, int b_off, const float* a, int nh, int nkv, int d, int dv, int taps, const float* conv_q, const float* conv_k, const float* conv_v, const float* a_log, const float* dt_bias, float q_scale, float* state, long long state_elems, const int* slots, const int* cu_q, const int* token_pos, const int* token_seq, const int* seq_lens, float* qkv, float* g, float* beta, float* out, int B, void* stream);
 
+// gated_state.cu
+int illm_mlstm_gates(const float* x, int T, int ld, int q_off, int k_off, int i_off, int f_off, const float* i_bias, const float* f_bias, float cap, float q_scale, int nh, int d, float* state, long long state_stride, long long n_off, long long m_off, const int* slots, const int* cu_q, float* ga, float* gb, float* scale, int B, void* stream);
+int illm_ssm_gates(const float* x, int T, int ld, int dt_off, const float* dt_bias, const float* a_log, int nh, float* ga, float* gb, void* stream);
+
+// layernorm.cu
+int illm_layernorm_sandwich(float* x, const float* y, const float* wb, const float* w, void* out, int out_dtype, const int* rows, int n_rows, int H, float eps, int write_x, void* stream);
+
+// short_conv.cu
+int illm_short_conv(const float* x, int T, int ldx, int x_off, int C, int taps, const float* w, const float* bias, int act, int residual, float* state, long long state_stride, long long state_off, const int* slots, const int* cu_q, const int* token_seq, int B, void* out, int out_dtype, int ldo, int o_off, int update_state, void* stream);
+
 // latent_attention.cu
 int illm_latent_prep(const float* x, int ld, int Q, int R, const float* wq, const float* wkv, float eps, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* cq_out, void* kc, int act_dtype, int T, int* err, void* stream);
 int illm_latent_attention_any(const void* q, const void* kc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int H, int R, int page_size, int window, float scale, void* stream);
@@ -55,6 +71,8 @@ int illm_head_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void*
 int illm_moe_max_tiles(int T, int top, int E, int bm);
 int illm_moe_row_tile(int T, int top, int tensor_cores);
 int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int bm, int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
+int illm_moe_route_ex(const float* logits, const float* bias, int T, int E, int top, int bm, int scoring, int groups, int keep, int renorm, int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
+int illm_moe_combine_plus(const float* rows, const int* row_of_pair, const float* weight, const float* plus, float* out, int T, int D, int top, void* stream);
 int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated, int act, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows, void* stream);
 int illm_moe_gather_rows(const void* x, void* xs, const int* pair_of_row, int P, int K, int top, void* stream);
 int illm_moe_combine(const float* rows, const int* row_of_pair, const float* weight, float* out, int T, int D, int top, void* stream);
@@ -70,6 +88,7 @@ int illm_join_rows(const float* a, const float* b, int H, void* y, int act_dtype
 
 // embedding.cu
 int illm_embedding(const int* ids, const void* table, int table_dtype, float* out, int T, int H, int V, int* err, void* stream);
+int illm_embedding_scaled(const int* ids, const int* token_pos, const void* table, int table_dtype, float* out, int T, int H, int V, float scale, const float* inv_freq, int* err, void* stream);
 int illm_set_pdl(int on);
 long long illm_launch_count();
 

@@ -51,6 +51,76 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
     for (int k = lane + 32; k < top; k += 32) weight[(size_t)t * top + k] /= sum;
 }
 
+// Routing by scores over ALL experts: s = softmax(z); the choice looks at s + choice_bias (the bias never enters the
+// weights), optionally confined to the `keep` best of `groups` equal groups of neighbouring experts (a group's score
+// is its largest choice score; experts of other groups cannot be chosen, whatever their score); the weights are the
+// chosen experts' s, divided by their sum only if `renorm`.  Among equal scores the lowest index wins.  A warp per
+// token; up to 32 groups.
+__global__ void moe_route_scored_kernel(const float* __restrict__ logits, const float* __restrict__ choice_bias, int T, int E, int top, int groups,
+                                        int keep, int renorm, int* __restrict__ expert, float* __restrict__ weight) {
+    pdl_grid_sync();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * E;
+    float zmax = -INFINITY;
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+    zmax = warp_max(zmax);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) den += expf(z[e] - zmax);
+    den = warp_sum(den);
+    const int per = E / groups;
+    unsigned kept = 0xffffffffu;       // bit g: group g may be chosen from
+    if (groups > 1 && keep < groups) {
+        float mine = -INFINITY;        // lane g holds group g's score
+        for (int g = 0; g < groups; g++) {
+            float best = -INFINITY;
+            for (int e = g * per + lane; e < (g + 1) * per; e += 32) best = fmaxf(best, expf(z[e] - zmax) / den + (choice_bias ? choice_bias[e] : 0.f));
+            best = warp_max(best);
+            if (lane == g) mine = best;
+        }
+        kept = 0;
+        for (int k = 0; k < keep; k++) {
+            float bv = (lane < groups && !((kept >> lane) & 1)) ? mine : -INFINITY;
+            int bi = (lane < groups && !((kept >> lane) & 1)) ? lane : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            kept |= 1u << bi;
+        }
+    }
+    float sum = 0.f;
+    for (int k = 0; k < top; k++) {
+        float bv = -INFINITY, bs = 0.f;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            if (!((kept >> (e / per)) & 1)) continue;
+            bool taken = false;
+            for (int j = 0; j < k; j++) taken |= expert[(size_t)t * top + j] == e;
+            if (taken) continue;
+            const float sc = expf(z[e] - zmax) / den;
+            const float v = sc + (choice_bias ? choice_bias[e] : 0.f);
+            if (v > bv || bi == 0x7fffffff) { bv = v; bi = e; bs = sc; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o), os = __shfl_xor_sync(0xffffffffu, bs, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; bs = os; }
+        }
+        sum += bs;
+        if (lane == 0) {
+            expert[(size_t)t * top + k] = bi;
+            weight[(size_t)t * top + k] = bs;
+        }
+        __syncwarp();
+    }
+    if (renorm)
+        for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] /= sum;
+}
+
 // dynamic shared memory: 3 E + 1 ints
 __global__ void __launch_bounds__(1024)
 moe_layout_kernel(const int* __restrict__ expert, int P, int E, int bm, int* __restrict__ row_of_pair, int* __restrict__ pair_of_row,
@@ -294,8 +364,9 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* 
             }
 }
 
+// plus: float32 [T, D] added to the experts' sum (a shared expert's output), or nullptr
 __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
-                                   float* __restrict__ out, int D, int top, long long n) {
+                                   const float* __restrict__ plus, float* __restrict__ out, int D, int top, long long n) {
     pdl_grid_sync();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -303,7 +374,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __
     const int c = (int)(i - t * D);
     float acc = 0.f;
     for (int k = 0; k < top; k++) acc = fmaf(weight[t * top + k], rows[(size_t)row_of_pair[t * top + k] * D + c], acc);
-    out[i] = acc;
+    out[i] = plus ? acc + plus[i] : acc;
 }
 
 extern "C" int illm_moe_max_tiles(int T, int top, int E, int bm) { return (int)(((long long)T * top + bm - 1) / bm) + E; }
@@ -325,14 +396,33 @@ extern "C" int illm_moe_gather_rows(const void* x, void* xs, const int* pair_of_
     return illm_launch_status();
 }
 
+extern "C" int illm_moe_route_ex(const float* logits, const float* bias, int T, int E, int top, int bm, int scoring, int groups, int keep, int renorm,
+                                 int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows,
+                                 void* stream);
 // logits [T, E] float32 (without the bias); expert, weight [T, top]; row_of_pair, pair_of_row [T * top];
 // tile_* [illm_moe_max_tiles(T, top, E, bm)], bm = illm_moe_row_tile(..)
 extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int bm, int* expert, float* weight, int* row_of_pair,
                               int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream) {
+    return illm_moe_route_ex(logits, bias, T, E, top, bm, 0, 1, 1, 1, expert, weight, row_of_pair, pair_of_row, tile_expert, tile_row0, tile_rows, stream);
+}
+
+// scoring 0: the `top` largest logits + bias, weights the softmax over the chosen; scoring 1: scores are the softmax
+// over all experts, bias enters the choice only, `keep` of `groups` groups may be chosen from, weights divided by
+// their sum if renorm (moe_route_scored_kernel)
+extern "C" int illm_moe_route_ex(const float* logits, const float* bias, int T, int E, int top, int bm, int scoring, int groups, int keep, int renorm,
+                                 int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows,
+                                 void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || (bm != 16 && bm != 64 && bm != 128) || (size_t)(3 * E + 1) * sizeof(int) > 160 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    illm_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, expert, weight);
+    if (scoring == 1) {
+        if (groups < 1 || groups > 32 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top) return ILLM_ERR_BAD_ARG;
+        illm_launch(moe_route_scored_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, groups, keep, renorm, expert, weight);
+    } else if (scoring == 0) {
+        illm_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, expert, weight);
+    } else {
+        return ILLM_ERR_BAD_ARG;
+    }
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     static bool raised = false;
     if (!raised) {
@@ -390,10 +480,14 @@ extern "C" int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dt
     return illm_launch_status();
 }
 
-extern "C" int illm_moe_combine(const float* rows, const int* row_of_pair, const float* weight, float* out, int T, int D, int top,
-                                void* stream) {
+extern "C" int illm_moe_combine_plus(const float* rows, const int* row_of_pair, const float* weight, const float* plus, float* out, int T, int D,
+                                     int top, void* stream) {
     if (T <= 0) return 0;
     const long long n = (long long)T * D;
-    illm_launch(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, rows, row_of_pair, weight, out, D, top, n);
+    illm_launch(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, rows, row_of_pair, weight, plus, out, D, top, n);
     return illm_launch_status();
+}
+extern "C" int illm_moe_combine(const float* rows, const int* row_of_pair, const float* weight, float* out, int T, int D, int top,
+                                void* stream) {
+    return illm_moe_combine_plus(rows, row_of_pair, weight, nullptr, out, T, D, top, stream);
 }

@@ -10,7 +10,8 @@
 //   q goes to q_out [T, nh d] in the activation dtype; k and v go into the token's place in the pages
 //       (k: [pages, nkv, page_size, d], v: [pages, nkv, page_size, dv]) if there are pages to write.
 //
-// A layer that attends to another layer's keys and values passes k_off < 0: only q is made.
+// A layer that attends to another layer's keys and values passes k_off < 0: only q is made.  A layer whose keys are
+// also its values passes v_off < 0: k alone is stored.
 // Everything is float32 until the stores.  One block per token; the sums have a fixed order.
 #include "common.cuh"
 
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(QkPrepArgs a) {
         const float v = e < a.rot ? rotated(buf + nq + (c - e), e, a.rot, a.pairs, cs) : buf[nq + c];
         ((TA*)a.kc)[(((size_t)page * a.nkv + hk) * a.page_size + slot) * a.d + e] = from_f32<TA>(v);
     }
+    if (a.v_off < 0) return;        // the keys are also the values: nothing else to store
     const int nv = a.nkv * a.dv;
     for (int c = threadIdx.x; c < nv; c += blockDim.x) {
         const int hk = c / a.dv, e = c - hk * a.dv;
@@ -118,7 +120,7 @@ extern "C" int illm_qk_prep(const void* x, int x_dtype, int ld, int q_off, int k
                             int page_size, void* q_out, void* kc, void* vc, int act_dtype, int T, int* err, void* stream) {
     if (T <= 0) return 0;
     if (nh <= 0 || d <= 0 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !q_out) return ILLM_ERR_BAD_ARG;
-    if (k_off >= 0 && (nkv <= 0 || dv <= 0 || v_off < 0)) return ILLM_ERR_BAD_ARG;
+    if (k_off >= 0 && (nkv <= 0 || dv <= 0)) return ILLM_ERR_BAD_ARG;      // v_off < 0 with k_off >= 0: keys alone are stored
     QkPrepArgs a{x, ld, q_off, k_off, v_off, nh, nkv, d, dv, bq, bk, bv, wq, wk, eps, cos_sin, rot, pairs, n_pos,
                  token_pos, token_seq, block_table, max_pages, page_size, q_out, kc, vc, err};
     const size_t smem = (size_t)(nh * d + (k_off >= 0 ? nkv * d : 0)) * sizeof(float);

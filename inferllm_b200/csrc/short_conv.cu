@@ -1,0 +1,72 @@
+// A short causal convolution over time, one filter per channel, across the steps of a sequence:
+//
+//   y_t[c] = act( sum_j w[c, j] * x_(t - taps + 1 + j)[c] + bias[c] )  (+ x_t[c], the residual form)
+//
+// x are channels [x_off, x_off + C) of the float32 rows [T, ldx] of one step; the rows before the step's first one
+// come from the sequence's state, the last taps - 1 input rows [taps - 1, C] (oldest first, zero for a new
+// sequence) at `state_off` of the sequence's slot.  The taps are added oldest first whether a row comes from the
+// step or from the state, so the result does not depend on how a prompt was cut.  short_conv_state_kernel renews
+// the state from the step's rows afterwards (a launch of its own: the convolution reads the old one).
+#include "common.cuh"
+
+struct ShortConvArgs {
+    const float* x;
+    int ldx, x_off, C, taps;
+    const float *w, *bias;
+    int act, residual;
+    float* state;
+    long long state_stride, state_off;
+    const int *slots, *cu_q, *token_seq;
+    void* out;
+    int ldo, o_off;
+};
+
+template <typename TO>
+__global__ void __launch_bounds__(256) short_conv_kernel(ShortConvArgs a) {
+    pdl_grid_sync();
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int b = a.token_seq[t], t0 = a.cu_q[b], i = t - t0, n_old = a.taps - 1;
+    const float* st = a.state + (size_t)a.slots[b] * a.state_stride + a.state_off;
+    float acc = 0.f;
+    for (int j = 0; j < a.taps; j++) {
+        const int s = i - n_old + j;
+        const float v = s >= 0 ? a.x[(size_t)(t0 + s) * a.ldx + a.x_off + c] : st[(size_t)(n_old + s) * a.C + c];
+        acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);
+    }
+    if (a.bias) acc += a.bias[c];
+    if (a.act == 1) acc = acc / (1.0f + expf(-acc));
+    if (a.residual) acc += a.x[(size_t)t * a.ldx + a.x_off + c];
+    ((TO*)a.out)[(size_t)t * a.ldo + a.o_off + c] = from_f32<TO>(acc);
+}
+
+// the last taps - 1 rows of (old state rows, then the step's rows), per sequence; a thread owns a channel and goes
+// through the rows oldest first, so that it reads an old row before it overwrites it
+__global__ void __launch_bounds__(256) short_conv_state_kernel(ShortConvArgs a) {
+    pdl_grid_sync();
+    const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int t0 = a.cu_q[b], n = a.cu_q[b + 1] - t0, n_old = a.taps - 1;
+    float* st = a.state + (size_t)a.slots[b] * a.state_stride + a.state_off;
+    for (int r = 0; r < n_old; r++) {
+        const int idx = n + r;      // place in (old rows, step rows)
+        st[(size_t)r * a.C + c] = idx < n_old ? st[(size_t)idx * a.C + c] : a.x[(size_t)(t0 + idx - n_old) * a.ldx + a.x_off + c];
+    }
+}
+
+// out_dtype: 0 float32, 1 bfloat16.  update_state != 0: the state is renewed after the convolution.
+extern "C" int illm_short_conv(const float* x, int T, int ldx, int x_off, int C, int taps, const float* w, const float* bias, int act, int residual,
+                               float* state, long long state_stride, long long state_off, const int* slots, const int* cu_q,
+                               const int* token_seq, int B, void* out, int out_dtype, int ldo, int o_off, int update_state, void* stream) {
+    if (T <= 0 || B <= 0) return 0;
+    if (C <= 0 || taps < 1 || !x || !w || !out || (taps > 1 && !state) || T > 0x7fffffff / 2) return ILLM_ERR_BAD_ARG;
+    ShortConvArgs a{x, ldx, x_off, C, taps, w, bias, act, residual, state, state_stride, state_off, slots, cu_q, token_seq, out, ldo, o_off};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int by = (C + 255) / 256;
+    if (by > 65535) return ILLM_ERR_BAD_ARG;
+    if (out_dtype == ILLM_BF16) illm_launch(short_conv_kernel<bf16>, dim3(T, by), dim3(256), 0, s, a);
+    else if (out_dtype == ILLM_F32) illm_launch(short_conv_kernel<float>, dim3(T, by), dim3(256), 0, s, a);
+    else return ILLM_ERR_BAD_ARG;
+    if (update_state && taps > 1) illm_launch(short_conv_state_kernel, dim3(B, by), dim3(256), 0, s, a);
+    return illm_launch_status();
+}

@@ -132,6 +132,47 @@ Mat embedding(Device& dev, const int* ids, long long T, const Mat& table, int* e
     return out;
 }
 
+Mat embedding_scaled(Device& dev, const StepView& ctx, const Mat& table, float scale, const float* inv_freq) {
+    need(table, "table");
+    Mat out = new_mat_exact(dev, ctx.T, table.cols, DType::F32);
+    check_kernel(illm_embedding_scaled(ctx.ids, ctx.token_pos, table.p, code_of(table.dtype, "embedding"), (float*)out.p, ctx.T, (int)table.cols,
+                                       (int)table.rows, scale, inv_freq, ctx.err, dev.stream()),
+                 "embedding_scaled");
+    return out;
+}
+
+Mat layernorm_sandwich(Device& dev, const Mat& resid, const Mat* delta, const Mat* post_w, const Mat* w, float eps, DType out_dtype, const int* rows,
+                       long long n_rows) {
+    need(resid, "the residual stream", true, DType::F32);
+    const long long H = resid.cols, n = rows ? n_rows : resid.rows;
+    if (delta) {
+        need(*delta, "the sublayer's output", true, DType::F32);
+        if (!post_w || post_w->dtype != DType::F32 || post_w->rows * post_w->cols != H || delta->rows != resid.rows || delta->cols != H)
+            throw KernelError("layernorm: the sublayer's output and its norm weight must be float32 of the stream's shape and width");
+    }
+    if (w && (w->dtype != DType::F32 || w->rows * w->cols != H)) throw KernelError("layernorm: the weight must be float32 of the stream's width");
+    if (H > kMaxNormWidth) throw KernelError("layernorm: rows of " + std::to_string(H) + " elements are beyond the kernel");
+    Mat y;
+    if (w) y = new_mat(dev, n, H, out_dtype);
+    check_kernel(illm_layernorm_sandwich((float*)resid.p, delta ? (const float*)delta->p : nullptr, delta ? (const float*)post_w->p : nullptr,
+                                         w ? (const float*)w->p : nullptr, w ? y.p : nullptr, w ? code_of(out_dtype, "layernorm") : 0, rows, (int)n,
+                                         (int)H, eps, rows == nullptr ? 1 : 0, dev.stream()),
+                 "layernorm_sandwich");
+    return y;
+}
+
+void short_conv(Device& dev, const Mat& x, const ShortConv& p, const StepView& ctx, const StateView& st, const Mat& out, int o_off) {
+    need(x, "the convolution's input", true, DType::F32);
+    if (p.C <= 0 || p.taps < 1 || p.x_off < 0 || p.x_off + p.C > x.cols || o_off < 0 || o_off + p.C > out.cols || out.rows != x.rows)
+        throw KernelError("short_conv: the channels do not lie inside the rows");
+    if (p.taps > 1 && (!st.state || st.dtype != DType::F32 || p.state_off < 0 || p.state_off + (long long)(p.taps - 1) * p.C > st.elements))
+        throw KernelError("short_conv: the cache entry does not hold the convolution's float32 rows");
+    check_kernel(illm_short_conv((const float*)x.p, (int)x.rows, (int)x.cols, p.x_off, p.C, p.taps, p.w, p.bias, p.act, p.residual ? 1 : 0,
+                                 (float*)st.state, st.elements, p.state_off, st.slots, ctx.cu_q, ctx.token_seq, ctx.B, out.p,
+                                 code_of(out.dtype, "short_conv"), (int)out.cols, o_off, p.update ? 1 : 0, dev.stream()),
+                 "short_conv");
+}
+
 Mat materialize(Device& dev, const Partials& p, DType dtype) {
     Mat out = new_mat_exact(dev, p.rows, p.cols, dtype);
     check_kernel(illm_splitk_reduce(p.ws, out.p, code_of(dtype, "splitk_reduce"), p.rows * p.cols, p.splits, dev.stream()), "splitk_reduce");
@@ -463,6 +504,65 @@ Mat decay_scan(Device& dev, const Mat& x, const DecayScan& p, const StepView& ct
     return out;
 }
 
+Mat gated_scan(Device& dev, const Mat& x, const GatedScan& p, const StepView& ctx, const StateView& st) {
+    need(x, "the packed projection", true, DType::F32);
+    if (p.n_heads <= 0 || p.n_qk_heads <= 0 || p.n_heads % p.n_qk_heads) throw KernelError("gated_scan: the heads must be a multiple of the query/key heads");
+    if (!st.state || st.dtype != DType::F32 || st.elements < (long long)p.n_heads * p.head_dim * p.v_head_dim)
+        throw KernelError("gated_scan: the cache entry does not hold float32 state of heads x head size x value size");
+    if (!decay_scan_supported(p.head_dim, p.v_head_dim)) throw KernelError("gated_scan: the head size is beyond the kernel (up to 1024)");
+    Mat out = new_mat_exact(dev, x.rows, (long long)p.n_heads * p.v_head_dim, DType::F32);
+    check_kernel(illm_gated_scan((const float*)x.p, (int)x.rows, (int)x.cols, p.q_off, p.k_off, p.v_off, p.n_heads, p.n_heads / p.n_qk_heads, p.head_dim,
+                                 p.v_head_dim, p.ga, p.gb, (float*)st.state, st.elements, st.slots, ctx.cu_q, (float*)out.p, ctx.B, dev.stream()),
+                 "gated_scan");
+    return out;
+}
+
+void mlstm_gates(Device& dev, const Mat& x, const MlstmGates& p, const StepView& ctx, const StateView& st, float* ga, float* gb, float* scale) {
+    need(x, "the packed projection", true, DType::F32);
+    if (!st.state || st.dtype != DType::F32 || p.n_off < 0 || p.m_off < 0 || p.n_off + (long long)p.n_heads * p.head_dim > st.elements ||
+        p.m_off + p.n_heads > st.elements)
+        throw KernelError("mlstm_gates: the cache entry does not hold the normaliser and the running maximum");
+    check_kernel(illm_mlstm_gates((const float*)x.p, (int)x.rows, (int)x.cols, p.q_off, p.k_off, p.i_off, p.f_off, p.i_bias, p.f_bias, p.cap, p.q_scale,
+                                  p.n_heads, p.head_dim, (float*)st.state, st.elements, p.n_off, p.m_off, st.slots, ctx.cu_q, ga, gb, scale, ctx.B,
+                                  dev.stream()),
+                 "mlstm_gates");
+}
+
+void ssm_gates(Device& dev, const Mat& x, int dt_off, const float* dt_bias, const float* a_log, int n_heads, float* ga, float* gb) {
+    need(x, "the packed projection", true, DType::F32);
+    check_kernel(illm_ssm_gates((const float*)x.p, (int)x.rows, (int)x.cols, dt_off, dt_bias, a_log, n_heads, ga, gb, dev.stream()), "ssm_gates");
+}
+
+Mat group_norm_gate_ex(Device& dev, const Mat& o, int group, const float* w, int w_len, float eps, const float* gate, int gate_ld, int gate_act,
+                       DType out_dtype, const NormGateExtras& ex) {
+    need(o, "the recurrence's output", true, DType::F32);
+    Mat y = new_mat(dev, o.rows, o.cols, out_dtype);
+    check_kernel(illm_group_norm_gate_ex((const float*)o.p, (int)o.rows, (int)o.cols, group, w, w_len > 0 ? w_len : (int)o.cols, eps, gate, gate_ld, gate_act,
+                                         ex.gate_first ? 1 : 0, ex.row_scale, ex.head, ex.skip_w, ex.skip_x, ex.skip_ld, y.p,
+                                         code_of(out_dtype, "group_norm_gate"), dev.stream()),
+                 "group_norm_gate");
+    return y;
+}
+
+bool attention_mixed_supported(DType dtype, int nh, int nkv, int d) {
+    return (dtype == DType::F32 || dtype == DType::BF16) && illm_attention_mixed_supported(nh, nkv, d, (int)dtype_size(dtype)) != 0;
+}
+
+Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const MixedAttention& m) {
+    need(q, "q");
+    if (kv.dtype != q.dtype || kv.n_kv_heads != g.n_kv_heads || kv.head_dim != g.head_dim || kv.v != kv.k)
+        throw KernelError("attention_mixed: needs a keys-only cache entry of this layer's head count and size, in the activation dtype");
+    if (!attention_mixed_supported(q.dtype, g.n_heads, g.n_kv_heads, g.head_dim))
+        throw KernelError("attention_mixed: " + std::to_string(g.n_heads) + " heads of " + std::to_string(g.head_dim) + " channels are beyond the kernel");
+    if (q.cols < (long long)g.n_heads * g.head_dim) throw KernelError("attention_mixed: q is narrower than heads x head size");
+    Mat out = new_mat(dev, q.rows, (long long)g.n_heads * g.head_dim, q.dtype);
+    check_kernel(illm_attention_mixed(q.p, (int)q.cols, kv.k, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, code_of(q.dtype, "attention_mixed"),
+                                      (int)q.rows, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size, kv.window, scale, m.r1, m.r2, m.mix, m.gate,
+                                      m.gate_stride, dev.stream()),
+                 "attention_mixed");
+    return out;
+}
+
 Mat group_norm_gate(Device& dev, const Mat& o, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act,
                     DType out_dtype, int w_len) {
     need(o, "the recurrence's output", true, DType::F32);
@@ -770,6 +870,12 @@ Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transpo
 }
 
 Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* router_bias, int E, int top, const Mat& w_gu, const Mat& w_down, int act) {
+    MoeRouting r;
+    r.bias = router_bias;
+    return moe_forward_ex(dev, h, logits, r, E, top, w_gu, w_down, act);
+}
+
+Mat moe_forward_ex(Device& dev, const Mat& h, const Mat& logits, const MoeRouting& r, int E, int top, const Mat& w_gu, const Mat& w_down, int act) {
     need(h, "h");
     need(logits, "the router's logits", true, DType::F32);
     const long long T = h.rows, D = h.cols;
@@ -791,8 +897,11 @@ Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* route
     int* tile_expert = dev.alloc_n<int>((size_t)tiles);
     int* tile_row0 = dev.alloc_n<int>((size_t)tiles);
     int* tile_rows = dev.alloc_n<int>((size_t)tiles);
-    check_kernel(illm_moe_route((const float*)logits.p, router_bias, (int)T, E, top, bm, expert, weight, row_of_pair, pair_of_row, tile_expert, tile_row0,
-                                tile_rows, dev.stream()),
+    if (r.scoring == 1 && (r.groups < 1 || r.groups > 32 || E % r.groups || r.keep < 1 || r.keep > r.groups || (long long)r.keep * (E / r.groups) < top))
+        throw KernelError("moe: the experts must form up to 32 equal groups, and the groups kept must hold at least `top` experts");
+    if (r.plus && (r.plus->dtype != DType::F32 || r.plus->rows != T || r.plus->cols != D)) throw KernelError("moe: the addend must be float32 [T, hidden]");
+    check_kernel(illm_moe_route_ex((const float*)logits.p, r.bias, (int)T, E, top, bm, r.scoring, r.groups, r.keep, r.renorm ? 1 : 0, expert, weight, row_of_pair,
+                                   pair_of_row, tile_expert, tile_row0, tile_rows, dev.stream()),
                  "moe_route");
     const int code = code_of(h.dtype, "moe");
     Mat hid = new_mat_exact(dev, P, F, h.dtype), rows = new_mat_exact(dev, P, D, DType::F32), out = new_mat_exact(dev, T, D, DType::F32);
@@ -813,7 +922,9 @@ Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* route
                                    tile_rows, dev.stream()),
                      "moe_gemm (down)");
     }
-    check_kernel(illm_moe_combine((const float*)rows.p, row_of_pair, weight, (float*)out.p, (int)T, (int)D, top, dev.stream()), "moe_combine");
+    check_kernel(illm_moe_combine_plus((const float*)rows.p, row_of_pair, weight, r.plus ? (const float*)r.plus->p : nullptr, (float*)out.p, (int)T, (int)D, top,
+                                       dev.stream()),
+                 "moe_combine");
     return out;
 }
 

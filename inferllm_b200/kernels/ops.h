@@ -119,6 +119,27 @@ std::string attention_kernels_for(DType dtype, int nh, int nkv, int d, int page_
 // ---- kernels
 
 Mat embedding(Device& dev, const int* ids, long long T, const Mat& table, int* err);
+// table[id] * scale plus, with inv_freq (float32 [ceil(H / 2)] on the device), the sinusoid position vector
+// (sin(p f_i), cos(p f_i)) in entries (2i, 2i + 1)
+Mat embedding_scaled(Device& dev, const StepView& ctx, const Mat& table, float scale, const float* inv_freq);
+// Layer norm (weight, no bias) around the float32 stream: resid += ln(delta) * post_w (delta, post_w nullptr: nothing
+// is added), then ln(resid) * w in `out_dtype` (w nullptr: the addition alone, an empty matrix comes back).  rows
+// (int32, device) gathers: only those rows are made and resid is left as it is.
+Mat layernorm_sandwich(Device& dev, const Mat& resid, const Mat* delta_f32, const Mat* post_w_f32, const Mat* w_f32, float eps, DType out_dtype,
+                       const int* rows, long long n_rows);
+// y = act(conv(x) + bias) (+ x): a causal convolution over time per channel of columns [x_off, x_off + C) of the
+// float32 rows x, `taps` taps w [C, taps] (float32, the last the token's own), the rows before the step from the
+// sequence's state ([taps - 1, C] at state_off of the slot's elements), which is renewed if `update`.  Written to
+// columns [o_off, o_off + C) of `out`.
+struct ShortConv {
+    int x_off = 0, C = 0, taps = 1;
+    const float *w = nullptr, *bias = nullptr;
+    int act = 0;              // 0: none, 1: silu
+    bool residual = false;
+    long long state_off = 0;
+    bool update = true;
+};
+void short_conv(Device& dev, const Mat& x_f32, const ShortConv& p, const StepView& ctx, const StateView& st, const Mat& out, int o_off);
 // y = rmsnorm(resid (+ delta)) * weight; resid is updated in place when write_resid.  rows (int32
 // [n_rows], device) gathers: only those rows are normed and y is [n_rows, H].
 Mat add_rmsnorm(Device& dev, const Mat& resid, const MatOrPartials* delta, const Mat& weight, float eps, DType out_dtype,
@@ -170,6 +191,15 @@ Mat attention_decode_ex(Device& dev, const Mat& qkv, const KVView& kv, const Ste
 // Attention with extras: the tensor-core prompt kernel and the split-key decode kernel where the
 // sizes allow (bfloat16, keys and values of one size, 64 or 128), the general kernel otherwise.
 Mat attention_ex(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const AttentionExtras& extras);
+// Attention whose heads' scores are mixed before the softmax (mix float32 [n_heads, n_heads] or nullptr), with a
+// logarithmic distance penalty r1_h ln(1 + r2_h (i - j)) (r1, r2 float32 [n_heads] or nullptr), over a keys-only
+// cache entry whose keys are also the values, and an element-wise sigmoid gate (float32 [T, gate_stride] or nullptr).
+struct MixedAttention {
+    const float *r1 = nullptr, *r2 = nullptr, *mix = nullptr, *gate = nullptr;
+    int gate_stride = 0;
+};
+bool attention_mixed_supported(DType dtype, int nh, int nkv, int d);
+Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const MixedAttention& m);
 // Attention of the step's tokens over a cache entry: picks the kernel for the dtype, head size and kind of step.
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
 
@@ -217,6 +247,41 @@ struct DecayScan {
 int decay_scan_segments(int B, int n_heads, int v_head_dim, int max_q, int n_sms);
 Mat decay_scan(Device& dev, const Mat& x_f32, const DecayScan& p, const StepView& ctx, const StateView& st);
 bool decay_scan_supported(int head_dim, int v_head_dim);
+// The same recurrence with a gate pair per token and head in place of the fixed decay: S_t = a_t S_(t-1) + b_t k_t v_t^T,
+// o_t = S_t^T q_t; ga, gb float32 [T, n_heads] on the device; n_qk_heads query/key heads shared by n_heads / n_qk_heads
+// value heads each; q, k, v are columns of x_f32 and read as they are.  The state block S [n_heads, dv, d] stands at
+// the start of the slot's elements (the entry may hold more behind it).  Always in order.
+struct GatedScan {
+    int q_off = 0, k_off = 0, v_off = 0;
+    int n_heads = 0, n_qk_heads = 0, head_dim = 0, v_head_dim = 0;
+    const float *ga = nullptr, *gb = nullptr;
+};
+Mat gated_scan(Device& dev, const Mat& x_f32, const GatedScan& p, const StepView& ctx, const StateView& st);
+// The gates of the matrix memory with exponential gating (csrc/gated_state.cu): from the input and forget logits at
+// i_off and f_off of x_f32 (+ biases, soft-capped) and the running maximum and normaliser kept at n_off / m_off of the
+// slot's elements, ga, gb and the output factor q_scale / (max(|q_scale n.q|, exp(-m)) + 1e-6), each float32 [T, heads].
+struct MlstmGates {
+    int q_off = 0, k_off = 0, i_off = 0, f_off = 0;
+    const float *i_bias = nullptr, *f_bias = nullptr;
+    float cap = 1.f, q_scale = 1.f;
+    int n_heads = 0, head_dim = 0;
+    long long n_off = 0, m_off = 0;
+};
+void mlstm_gates(Device& dev, const Mat& x_f32, const MlstmGates& p, const StepView& ctx, const StateView& st, float* ga, float* gb, float* scale);
+// dt = softplus(x[dt_off + h] + dt_bias[h]); ga = exp(-exp(a_log[h]) dt); gb = dt
+void ssm_gates(Device& dev, const Mat& x_f32, int dt_off, const float* dt_bias, const float* a_log, int n_heads, float* ga, float* gb);
+// group_norm_gate with what some recurrences put before the norm: a factor per token and head on o (row_scale
+// [T, heads]), a skip term skip_w[head] * skip_x[t, column] (skip_x float32 rows skip_ld apart), and the gate before
+// the norm instead of behind it (gate_first)
+struct NormGateExtras {
+    const float* row_scale = nullptr;
+    int head = 0;                 // columns per head
+    const float *skip_w = nullptr, *skip_x = nullptr;
+    int skip_ld = 0;
+    bool gate_first = false;
+};
+Mat group_norm_gate_ex(Device& dev, const Mat& o_f32, int group, const float* w, int w_len, float eps, const float* gate, int gate_ld, int gate_act,
+                       DType out_dtype, const NormGateExtras& ex);
 // y = o / sqrt(mean over groups of `group` columns (o^2) + eps) (* w) * act(gate), gate_act 1: silu, 2: sigmoid;
 // w has w_len entries (0: the whole row), a shorter one repeats along the row (one group's weight for every group)
 Mat group_norm_gate(Device& dev, const Mat& o_f32, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act,
@@ -267,6 +332,18 @@ Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transpo
 // (per expert, rows 2i and 2i + 1 are gate and up of output i), w_down [experts * hidden, ff].  Returns float32 [T, hidden].
 Mat moe_forward(Device& dev, const Mat& h, const Mat& logits_f32, const float* router_bias, int experts, int top, const Mat& w_gate_up,
                 const Mat& w_down, int act);
+// How the experts are chosen and weighted.  scoring 0: the largest logits (+ bias), weights the softmax over the chosen;
+// scoring 1: scores are the softmax over all experts, `bias` enters the choice only, the experts form `groups` equal
+// groups of neighbours of which the `keep` best (by their largest choice score) may be chosen from, and the weights
+// are the chosen scores, divided by their sum only if `renorm`.  plus: float32 [T, hidden] added to the result.
+struct MoeRouting {
+    int scoring = 0, groups = 1, keep = 1;
+    bool renorm = true;
+    const float* bias = nullptr;
+    const Mat* plus = nullptr;
+};
+Mat moe_forward_ex(Device& dev, const Mat& h, const Mat& logits_f32, const MoeRouting& r, int experts, int top, const Mat& w_gate_up,
+                   const Mat& w_down, int act);
 
 // float32 [B, V] -> int32 [B], the lowest id among equal maxima.
 int* argmax(Device& dev, const float* logits, long long B, long long V, int* out /* nullptr: from the arena */);

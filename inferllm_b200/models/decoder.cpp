@@ -70,7 +70,12 @@ void DecoderModel::load_tensors(const std::function<std::unique_ptr<TensorSource
 std::map<int, CacheRequest> DecoderModel::cache_requests() const {
     std::map<int, CacheRequest> out;
     for (const ScheduleEntry& e : spec.schedule)
-        if (e.writes) out[e.cache] = layers_[(size_t)e.layer].mixer->cache_request();
+        if (e.writes) {
+            out[e.cache] = layers_[(size_t)e.layer].mixer->cache_request();
+            const CacheRequest aux = layers_[(size_t)e.layer].mixer->aux_cache_request();
+            if (aux.kind == CacheRequest::FixedState) out[kAuxCacheEntryBase + e.cache] = aux;
+            else if (aux.kind != CacheRequest::None) throw ConfigError("a mixer's second cache entry must be fixed state");
+        }
     const CacheRequest er = embedding_->cache_request();
     if (er.kind != CacheRequest::None) out[kEmbeddingCacheEntry] = er;
     return out;
@@ -119,6 +124,10 @@ Mat DecoderModel::forward(const StepContext& ctx, const SequenceCache& cache, co
                 view.st = cache.state_view(e.cache, ctx.slots);
                 break;
             default: break;
+        }
+        if (cache.kind_of(kAuxCacheEntryBase + e.cache) == SequenceCache::State) {
+            view.has_aux = true;
+            view.aux = cache.state_view(kAuxCacheEntryBase + e.cache, ctx.slots);
         }
         layers_[(size_t)e.layer].block->forward(stream, ctx, view, e.writes);
     }

@@ -20,6 +20,8 @@ class SequenceCache;
 
 // The cache entry number of an embedding that keeps per-sequence state (schedule entries count from 0).
 constexpr int kEmbeddingCacheEntry = -1;
+// A mixer's second entry (Mixer::aux_cache_request) has the number of its first plus this.
+constexpr int kAuxCacheEntryBase = 1 << 20;
 
 class DecoderModel {
 public:

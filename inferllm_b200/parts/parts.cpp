@@ -8,6 +8,9 @@ void register_decay_parts(std::map<std::string, PartFactory<Mixer>>& mixers);   
 void register_delta_parts(std::map<std::string, PartFactory<Mixer>>& mixers);      // parts/delta_mixer.cpp
 void register_latent_parts(std::map<std::string, PartFactory<Mixer>>& mixers);     // parts/latent_mixer.cpp
 void register_routed_parts(std::map<std::string, PartFactory<FeedForward>>& ffs);  // parts/routed_mlp.cpp
+void register_gated_state_parts(std::map<std::string, PartFactory<Mixer>>& mixers);   // parts/gated_mixers.cpp
+void register_sandwich_parts(std::map<std::string, PartFactory<Norm>>& norms, std::map<std::string, PartFactory<Mixer>>& mixers,
+                             std::map<std::string, BlockKind>& blocks);               // parts/sandwich.cpp
 
 // ---- registries
 
@@ -336,36 +339,58 @@ struct NoPosition : PositionEncoding {
 // the part's prefix).  With any of the first six the layer takes the general path: one float32
 // product for q, k, v and the gate, one kernel for biases, norms, rotation and the cache write
 // (ops::qk_prep), and the general attention kernel, which knows sinks, gates and value sizes.
+//
+// A second family of options changes the scores themselves and takes a kernel of its own (ops::attention_mixed):
+// `values` = "keys" (there is no value projection: the values are the keys as projected, and the cache entry keeps
+// keys only), `distance_bias` = "log1p" (r1_h ln(1 + r2_h (i - j)) is taken off the score of query i and key j; two
+// numbers per head, tensors "r1" and "r2"), `head_mix` = true (before the softmax the heads' scores are mixed,
+// score_h <- sum_g M[h, g] score_g, tensor "mix" [heads, heads]) and `out_gate` = "sigmoid" (a full-width gate
+// projection of the mixer's input; the concatenated heads are multiplied by its sigmoid element by element).  The
+// last three need the first.
 struct Attention : Mixer {
     long long hidden;
     int n_heads, n_kv_heads, head_dim, v_head_dim, window;
     float scale, norm_eps;
     bool qkv_bias, proj_norm, has_sink, has_gate, own_kv, out_f32;
+    bool values_are_keys, log_distance, head_mix, wide_gate;
     std::map<std::string, std::string> names;
     std::unique_ptr<PositionEncoding> position;
     DeviceBuffer qkv_buf, o_buf;
     Mat w_qkv, w_o;
-    OwnedMat b_q, b_k, b_v, n_q, n_k, sinks;
+    OwnedMat b_q, b_k, b_v, n_q, n_k, sinks, dist_r1, dist_r2, mix;
     Attention(const PartSpec& s, Runtime* rt)
             : Mixer(s, rt), hidden(s.get_int("hidden_size")), n_heads((int)s.get_int("n_heads")), n_kv_heads((int)s.get_int("n_kv_heads")),
               head_dim((int)s.get_int("head_dim")), v_head_dim((int)s.get_int("v_head_dim", s.get_int("head_dim"))),
               window((int)s.get_int("window", 0)), norm_eps((float)s.get_double("norm_eps", 1e-6)), qkv_bias(s.get_bool("qkv_bias", false)),
               proj_norm(s.get_string("qk_norm", "none") == "projection"), has_sink(s.get_bool("sink", false)),
               has_gate(s.get_string("out_gate", "none") == "head_sigmoid"), own_kv(s.get_bool("own_kv", true)),
-              out_f32(s.get_string("output_dtype", "compute") == "float32") {
+              out_f32(s.get_string("output_dtype", "compute") == "float32"), values_are_keys(s.get_string("values", "own") == "keys"),
+              log_distance(s.get_string("distance_bias", "none") == "log1p"), head_mix(s.get_bool("head_mix", false)),
+              wide_gate(s.get_string("out_gate", "none") == "sigmoid") {
         if (hidden <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || v_head_dim <= 0 || window < 0)
             throw ConfigError("attention: sizes must be positive");
         if (n_heads % n_kv_heads) throw ConfigError("attention: n_heads must be a multiple of n_kv_heads");
         const std::string qn = s.get_string("qk_norm", "none"), og = s.get_string("out_gate", "none");
         if (qn != "none" && qn != "projection") throw ConfigError("attention: qk_norm '" + qn + "' is not supported (none, projection)");
-        if (og != "none" && og != "head_sigmoid") throw ConfigError("attention: out_gate '" + og + "' is not supported (none, head_sigmoid)");
+        if (og != "none" && og != "head_sigmoid" && og != "sigmoid")
+            throw ConfigError("attention: out_gate '" + og + "' is not supported (none, head_sigmoid, sigmoid)");
+        const std::string vs = s.get_string("values", "own"), db = s.get_string("distance_bias", "none");
+        if (vs != "own" && vs != "keys") throw ConfigError("attention: values '" + vs + "' is not supported (own, keys)");
+        if (db != "none" && db != "log1p") throw ConfigError("attention: distance_bias '" + db + "' is not supported (none, log1p)");
+        if ((log_distance || head_mix || wide_gate) && !values_are_keys)
+            throw ConfigError("attention: distance_bias, head_mix and the element-wise gate run on the kernel for values = keys only");
+        if (values_are_keys && (v_head_dim != head_dim || !own_kv || qkv_bias || proj_norm || has_sink || has_gate))
+            throw ConfigError("attention: values = keys needs key and value heads of one size and takes no biases, projection norms, sinks or head gates");
+        if (rt && values_are_keys && !ops::attention_mixed_supported(rt->dtype, n_heads, n_kv_heads, head_dim))
+            throw ConfigError("attention: " + std::to_string(n_heads) + " heads of " + std::to_string(head_dim) +
+                              " channels are beyond the kernel for mixed scores (heads x head size up to 8192)");
         names = {{"q", "q_proj.weight"}, {"k", "k_proj.weight"}, {"v", "v_proj.weight"}, {"o", "o_proj.weight"},
                  {"q_bias", "q_proj.bias"}, {"k_bias", "k_proj.bias"}, {"v_bias", "v_proj.bias"}, {"q_norm", "q_norm.weight"},
-                 {"k_norm", "k_norm.weight"}, {"sink", "sinks"}, {"gate", "gate_proj.weight"}};
+                 {"k_norm", "k_norm.weight"}, {"sink", "sinks"}, {"gate", "gate_proj.weight"}, {"r1", "r1"}, {"r2", "r2"}, {"mix", "mix"}};
         if (s.has("names"))
             for (auto& m : s.params.at("names").members()) names[m.first] = m.second.as_string();
         // the attention kernels read heads 16 bytes at a time: said when the model is built, not at its first step
-        if (rt && !general() && head_dim % 8)
+        if (rt && !general() && !values_are_keys && head_dim % 8)
             throw ConfigError("attention: head size " + std::to_string(head_dim) +
                               " is not supported by the kernels (multiples of 8 up to " + std::to_string(ops::kMaxHeadDimGeneric) + ")");
         if (rt && (head_dim > ops::kMaxHeadDimGeneric || v_head_dim > ops::kMaxHeadDimGeneric) && !(head_dim == 64 || head_dim == 128))
@@ -379,6 +404,7 @@ struct Attention : Mixer {
     bool general() const {
         return v_head_dim != head_dim || qkv_bias || proj_norm || has_sink || has_gate || !own_kv || out_f32;
     }
+    long long gate_rows() const { return has_gate ? n_heads : wide_gate ? (long long)n_heads * v_head_dim : 0; }
     bool graph_safe() const override { return true; }     // a decode step's launches depend only on the batch size
     // Causal attention: tokens behind a sequence's real ones are seen by none of them.  Said only for
     // the plain case: no window, and a position encoding that is nothing but the table rotation (any
@@ -387,7 +413,7 @@ struct Attention : Mixer {
         const float* t;
         int rot;
         long long n;
-        return window == 0 && position->rotation_table(&t, &rot, &n);
+        return window == 0 && !values_are_keys && position->rotation_table(&t, &rot, &n);
     }
     TensorDecls tensors() const override {
         const long long q = (long long)n_heads * head_dim, k = (long long)n_kv_heads * head_dim, v = (long long)n_kv_heads * v_head_dim;
@@ -399,7 +425,7 @@ struct Attention : Mixer {
         if (own_kv) {
             d.push_back({nm("k"), TensorDecl{{k, hidden}}});
             if (qkv_bias) d.push_back({nm("k_bias"), TensorDecl{{k}}});
-            d.push_back({nm("v"), TensorDecl{{v, hidden}}});
+            if (!values_are_keys) d.push_back({nm("v"), TensorDecl{{v, hidden}}});
             if (qkv_bias) d.push_back({nm("v_bias"), TensorDecl{{v}}});
         }
         if (proj_norm) {
@@ -407,15 +433,20 @@ struct Attention : Mixer {
             if (own_kv) d.push_back({nm("k_norm"), TensorDecl{{k}, "norm"}});
         }
         if (has_sink) d.push_back({nm("sink"), TensorDecl{{(long long)n_heads}}});
-        if (has_gate) d.push_back({nm("gate"), TensorDecl{{(long long)n_heads, hidden}}});
+        if (has_gate || wide_gate) d.push_back({nm("gate"), TensorDecl{{gate_rows(), hidden}}});
+        if (log_distance) {
+            d.push_back({nm("r1"), TensorDecl{{(long long)n_heads}}});
+            d.push_back({nm("r2"), TensorDecl{{(long long)n_heads}}});
+        }
+        if (head_mix) d.push_back({nm("mix"), TensorDecl{{(long long)n_heads, (long long)n_heads}}});
         d.push_back({nm("o"), TensorDecl{{hidden, o}}});
         return d;
     }
     // rows of the packed matrix: q, then k and v (a layer with keys and values of its own), then the gate
     long long q_rows() const { return (long long)n_heads * head_dim; }
     long long k_rows() const { return own_kv ? (long long)n_kv_heads * head_dim : 0; }
-    long long v_rows() const { return own_kv ? (long long)n_kv_heads * v_head_dim : 0; }
-    long long packed_rows() const { return q_rows() + k_rows() + v_rows() + (has_gate ? n_heads : 0); }
+    long long v_rows() const { return own_kv && !values_are_keys ? (long long)n_kv_heads * v_head_dim : 0; }
+    long long packed_rows() const { return q_rows() + k_rows() + v_rows() + gate_rows(); }
     void load(TensorSource& src) override {
         const long long q = q_rows(), k = k_rows(), v = v_rows(), all = packed_rows();
         const size_t es = dtype_size(rt->dtype);
@@ -424,9 +455,9 @@ struct Attention : Mixer {
         src.fetch_into(names.at("q"), w_qkv.p, rt->dtype);
         if (own_kv) {
             src.fetch_into(names.at("k"), (char*)w_qkv.p + (size_t)q * hidden * es, rt->dtype);
-            src.fetch_into(names.at("v"), (char*)w_qkv.p + (size_t)(q + k) * hidden * es, rt->dtype);
+            if (!values_are_keys) src.fetch_into(names.at("v"), (char*)w_qkv.p + (size_t)(q + k) * hidden * es, rt->dtype);
         }
-        if (has_gate) src.fetch_into(names.at("gate"), (char*)w_qkv.p + (size_t)(q + k + v) * hidden * es, rt->dtype);
+        if (has_gate || wide_gate) src.fetch_into(names.at("gate"), (char*)w_qkv.p + (size_t)(q + k + v) * hidden * es, rt->dtype);
         const long long o = (long long)n_heads * v_head_dim;
         o_buf = DeviceBuffer(rt->dev, (size_t)hidden * o * es, "the output matrix of an attention layer");
         w_o = Mat{o_buf.get(), hidden, o, rt->dtype, hidden};
@@ -444,9 +475,48 @@ struct Attention : Mixer {
             if (own_kv) n_k = fetch_owned(rt, src, names.at("k_norm"), DType::F32, "a projection norm's weight");
         }
         if (has_sink) sinks = fetch_owned(rt, src, names.at("sink"), DType::F32, "the attention sinks");
+        if (log_distance) {
+            dist_r1 = fetch_owned(rt, src, names.at("r1"), DType::F32, "an attention layer's distance factors");
+            dist_r2 = fetch_owned(rt, src, names.at("r2"), DType::F32, "an attention layer's distance factors");
+        }
+        if (head_mix) mix = fetch_owned(rt, src, names.at("mix"), DType::F32, "an attention layer's head-mixing matrix");
     }
     CacheRequest cache_request() const override {
+        if (values_are_keys) return CacheRequest::paged_keys_only(n_kv_heads, head_dim, window);
         return own_kv ? CacheRequest::paged(n_kv_heads, head_dim, window, v_head_dim) : CacheRequest();
+    }
+
+    // values = keys: one float32 product for q, k and the gate; q out and k into the pages (with the table rotation,
+    // if the layer has one); the kernel for mixed scores
+    MatOrPartials forward_mixed(const Mat& h, const StepContext& ctx, KVView kv, bool may_defer) {
+        Device& dev = *rt->dev;
+        const ops::Geometry g{n_heads, n_kv_heads, head_dim};
+        Mat x = ops::linear(dev, rt->gemm, h, w_qkv, DType::F32, false).m;
+        ops::QkPrep p;
+        p.q_off = 0;
+        p.k_off = (int)q_rows();
+        p.v_off = -1;
+        const float* table = nullptr;
+        int rot = 0;
+        long long n_pos = 0;
+        bool pairs = false;
+        if (!position->table_rotation(&table, &rot, &n_pos, &pairs))
+            throw EngineError("attention: with values = keys the position encoding must be none or a table rotation");
+        p.cos_sin = table;
+        p.rot_dim = rot;
+        p.pairs = pairs;
+        p.n_pos = n_pos;
+        Mat q = ops::qk_prep(dev, x, p, g, ctx, kv, rt->dtype);
+        ops::MixedAttention m;
+        m.r1 = (const float*)dist_r1.m.p;
+        m.r2 = (const float*)dist_r2.m.p;
+        m.mix = (const float*)mix.m.p;
+        if (wide_gate) {
+            m.gate = (const float*)x.p + (q_rows() + k_rows());
+            m.gate_stride = (int)x.cols;
+        }
+        Mat o = ops::attention_mixed(dev, q, kv, ctx, g, scale, m);
+        return ops::linear(dev, rt->gemm, o, w_o, out_f32 ? DType::F32 : rt->dtype, may_defer);
     }
 
     MatOrPartials forward_general(const Mat& h, const StepContext& ctx, KVView kv, bool may_defer) {
@@ -495,6 +565,7 @@ struct Attention : Mixer {
         Device& dev = *rt->dev;
         KVView kv = cache.kv;
         kv.writes = writes;
+        if (values_are_keys) return forward_mixed(h, ctx, kv, may_defer);
         if (general()) return forward_general(h, ctx, kv, may_defer);
         const ops::Geometry g{n_heads, n_kv_heads, head_dim};
         const float* table = nullptr;
@@ -567,18 +638,38 @@ struct GatedMLP : FeedForward {
 
 // Token embedding: x[t] = W[id[t]] (src/kern/naive/naive.cpp:43-54; EmbdModule, src/core/graph.cpp:143-151),
 // written as the float32 residual stream.
+// Two parameters beyond the gather: `scale` (the row times a constant) and `sinusoid_base` (a position vector is added:
+// entry 2i is sin(p base^(-2i / hidden)) and entry 2i + 1 the cosine of the same angle; the frequencies are made in
+// float64 once, angle and functions are float32).  A tied head still reads the table itself, without the scale.
 struct Embedding : EmbeddingPart {
     long long vocab, hidden;
     std::string tensor;         // the table's name below the part's prefix
+    double scale, sinusoid_base;
     OwnedMat weight;
+    DeviceBuffer freq_buf;
     Embedding(const PartSpec& s, Runtime* rt)
-            : EmbeddingPart(s, rt), vocab(s.get_int("vocab_size")), hidden(s.get_int("hidden_size")), tensor(s.get_string("tensor", "weight")) {}
+            : EmbeddingPart(s, rt), vocab(s.get_int("vocab_size")), hidden(s.get_int("hidden_size")), tensor(s.get_string("tensor", "weight")),
+              scale(s.get_double("scale", 1.0)), sinusoid_base(s.get_double("sinusoid_base", 0.0)) {
+        if (sinusoid_base < 0 || (s.has("sinusoid_base") && !(sinusoid_base > 0))) throw ConfigError("embedding: sinusoid_base must be positive");
+    }
     TensorDecls tensors() const override { return {{tensor, TensorDecl{{vocab, hidden}}}}; }
-    void load(TensorSource& src) override { weight = fetch_owned(rt, src, tensor, rt->dtype, "the embedding table"); }
+    void load(TensorSource& src) override {
+        weight = fetch_owned(rt, src, tensor, rt->dtype, "the embedding table");
+        if (sinusoid_base > 0) {
+            std::vector<float> f((size_t)(hidden + 1) / 2);
+            for (size_t i = 0; i < f.size(); i++) f[i] = (float)std::pow(sinusoid_base, -2.0 * (double)i / (double)hidden);
+            freq_buf = DeviceBuffer(rt->dev, f.size() * sizeof(float), "the frequencies of a sinusoid position vector");
+            rt->dev->synchronize();
+            check_cuda(cudaMemcpy(freq_buf.get(), f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice), "uploading the frequencies");
+        }
+    }
     ResidualStream forward(const StepContext& ctx) override {
         ResidualStream s;
         s.dev = rt->dev;
-        s.x = ops::embedding(*rt->dev, ctx.ids, ctx.T, weight.m, ctx.err);
+        if (scale != 1.0 || sinusoid_base > 0)
+            s.x = ops::embedding_scaled(*rt->dev, ctx, weight.m, (float)scale, (const float*)freq_buf.get());
+        else
+            s.x = ops::embedding(*rt->dev, ctx.ids, ctx.T, weight.m, ctx.err);
         return s;
     }
     const Mat* table() const override { return &weight.m; }
@@ -727,6 +818,8 @@ void register_builtin_parts() {
     register_delta_parts(reg<Mixer>());
     register_latent_parts(reg<Mixer>());
     register_routed_parts(reg<FeedForward>());
+    register_gated_state_parts(reg<Mixer>());
+    register_sandwich_parts(reg<Norm>(), reg<Mixer>(), block_reg());
     block_reg()["parallel"] = BlockKind{{"norm1"}, [] { return std::unique_ptr<Block>(new ParallelBlock); }};
     reg<FeedForward>()["linear"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<FeedForward>(new LinearMap(s, rt)); };
     reg<EmbeddingPart>()["bigram_embedding"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<EmbeddingPart>(new BigramEmbedding(s, rt)); };

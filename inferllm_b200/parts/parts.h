@@ -122,21 +122,33 @@ struct CacheView {
     enum Kind { None, KV, State } kind = None;
     KVView kv;
     StateView st;
+    // the second, fixed-state entry of a mixer that asked for one (Mixer::aux_cache_request)
+    bool has_aux = false;
+    StateView aux;
 };
 
 // The float32 residual stream [T, H] with an addition pending (or two: the sublayers of a parallel block).  A part's
 // output is not added at once: the next norm adds it while it reads the row anyway (one kernel for add + norm), which is
 // also where the sum is rounded: never, it stays float32.
+class Norm;
 struct ResidualStream {
     Device* dev = nullptr;
     Mat x;
     bool has_pending = false, has_pending2 = false;
     MatOrPartials pending, pending2;
+    // a norm that the pending addition passes on its way into the stream (a block that norms a sublayer's output):
+    // x + pending_post(pending); the next norm of the same kind does both in one kernel, flush() asks the norm itself
+    Norm* pending_post = nullptr;
     Mat h;      // the stream's rows in the compute dtype, where a block keeps them (norm after the sum); empty otherwise
     void add(const MatOrPartials& delta) {
         if (has_pending || has_pending2) flush();
         pending = delta;
         has_pending = true;
+    }
+    // x + post(delta): delta a finished float32 matrix
+    void add_normed(const MatOrPartials& delta, Norm* post) {
+        add(delta);
+        pending_post = post;
     }
     // A second addition behind a pending one, both finished matrices: x + pending + delta, added in that order by flush()
     // or by a norm that folds both in.  Anything else is added like add().
@@ -148,12 +160,7 @@ struct ResidualStream {
             add(delta);
         }
     }
-    Mat& flush() {
-        if (has_pending) ops::residual_add(*dev, x, pending);
-        if (has_pending2) ops::residual_add(*dev, x, pending2);
-        has_pending = has_pending2 = false;
-        return x;
-    }
+    Mat& flush();
 };
 
 class Norm : public Part {
@@ -168,7 +175,23 @@ public:
     // false for a norm whose optional weight was not in the file: the block leaves the norm out
     virtual bool present() const { return true; }
     virtual Mat forward_into_stream(ResidualStream& stream) { throw EngineError("norm '" + spec.kind + "' cannot replace the stream by its output"); }
+    // stream.x += norm(stream.pending), for the norm a sublayer's output passes before it joins the stream
+    // (ResidualStream::add_normed); only norms that can stand there override it.
+    virtual void add_normed_pending(ResidualStream& stream) { throw EngineError("norm '" + spec.kind + "' cannot norm a sublayer's output into the stream"); }
 };
+
+inline Mat& ResidualStream::flush() {
+    if (has_pending && pending_post) {
+        Norm* post = pending_post;
+        pending_post = nullptr;
+        post->add_normed_pending(*this);       // adds and clears the pending addition
+    }
+    if (has_pending) ops::residual_add(*dev, x, pending);
+    if (has_pending2) ops::residual_add(*dev, x, pending2);
+    has_pending = has_pending2 = false;
+    pending_post = nullptr;
+    return x;
+}
 
 class PositionEncoding : public Part {
 public:
@@ -210,6 +233,9 @@ public:
     // single prompts to whole buckets of tokens and replays them from captured graphs.
     virtual bool pad_safe() const { return false; }
     virtual CacheRequest cache_request() const { return CacheRequest(); }
+    // A second cache entry, of fixed per-sequence state, beside the first (a mixer with keys and values AND a few
+    // rows of state, say): the decoder gives it an entry number of its own and hands it over as CacheView::aux.
+    virtual CacheRequest aux_cache_request() const { return CacheRequest(); }
     // h [T, H] in the compute dtype -> [T, H].  `may_defer`: the result may be the unreduced slices of
     // a split matrix product, for a caller that only adds it to the residual stream.
     virtual MatOrPartials forward(const Mat& h, const StepContext& ctx, const CacheView& cache, bool writes, bool may_defer) = 0;

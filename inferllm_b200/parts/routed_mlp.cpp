@@ -9,6 +9,14 @@
 // grouped by expert on the device (nothing of the routing comes back to the host), so a step launches the same
 // kernels whatever the router decides.  Tensor names: `names` gives "router", "router_bias", the experts' prefix
 // "expert" (followed by the expert's number and a dot) and "gate", "up", "down" below it.
+//
+// A second way to choose, `scoring` = "softmax_all": the scores are s = softmax(z) over ALL experts; the `top` experts
+// with the largest s + correction are chosen (the correction, tensor "correction" [experts], present if
+// `choice_correction`, never enters the weights); with `groups` {count, keep} the experts form `count` equal groups of
+// neighbours, a group's score is its largest corrected score, and only experts of the `keep` best groups can be
+// chosen; the weights are the chosen experts' s, as they are unless `renormalize`.  `shared` {intermediate_size,
+// activation, names} adds a gated feed-forward that every token goes through (a "gated_mlp" part below the prefix
+// `shared_prefix`), its float32 output summed with the experts' in the kernel that combines them.
 #include "parts/parts.h"
 
 namespace illm {
@@ -19,6 +27,11 @@ struct RoutedMLP : FeedForward {
     long long hidden, inter;
     int experts, top, act;
     bool has_bias;
+    bool score_all, has_correction, renorm;
+    int groups = 1, keep = 1;
+    std::unique_ptr<FeedForward> shared;
+    std::string shared_prefix;
+    OwnedMat correction;
     std::map<std::string, std::string> names;
     DeviceBuffer gu_buf, down_buf;
     Mat w_gate_up, w_down;
@@ -26,11 +39,33 @@ struct RoutedMLP : FeedForward {
 
     RoutedMLP(const PartSpec& s, Runtime* rt)
             : FeedForward(s, rt), hidden(s.get_int("hidden_size")), inter(s.get_int("intermediate_size")), experts((int)s.get_int("experts")),
-              top((int)s.get_int("top")), act(ops::gate_act_from_name(s.get_string("activation", "silu"))), has_bias(s.get_bool("router_bias", false)) {
+              top((int)s.get_int("top")), act(ops::gate_act_from_name(s.get_string("activation", "silu"))), has_bias(s.get_bool("router_bias", false)),
+              score_all(s.get_string("scoring", "softmax_chosen") == "softmax_all"), has_correction(s.get_bool("choice_correction", false)),
+              renorm(s.get_bool("renormalize", false)), shared_prefix(s.get_string("shared_prefix", "shared.")) {
+        const std::string sc = s.get_string("scoring", "softmax_chosen");
+        if (sc != "softmax_chosen" && sc != "softmax_all") throw ConfigError("routed_mlp: scoring '" + sc + "' is not supported (softmax_chosen, softmax_all)");
+        if (!score_all && (has_correction || s.has("groups"))) throw ConfigError("routed_mlp: a choice correction and groups need scoring = softmax_all");
+        if (score_all && has_bias) throw ConfigError("routed_mlp: scoring = softmax_all takes a choice correction, not a router bias");
+        if (s.has("groups")) {
+            const Json& g = s.params.at("groups");
+            if (!g.is_object() || !g.has("count") || !g.has("keep") || !g.at("count").is_int() || !g.at("keep").is_int())
+                throw ConfigError("routed_mlp: groups must be {count, keep}");
+            groups = (int)g.at("count").as_int();
+            keep = (int)g.at("keep").as_int();
+            if (groups < 1 || groups > 32 || s.get_int("experts") % groups || keep < 1 || keep > groups ||
+                (long long)keep * (s.get_int("experts") / groups) < s.get_int("top"))
+                throw ConfigError("routed_mlp: the experts must form 1 to 32 equal groups, and the groups kept must hold at least `top` experts");
+        }
+        if (s.has("shared")) {
+            PartSpec sh("gated_mlp", s.params.at("shared"));
+            sh.params.set("hidden_size", s.get_int("hidden_size"));
+            sh.params.set("output_dtype", std::string("float32"));
+            shared = build_feed_forward(sh, rt);
+        }
         if (hidden <= 0 || inter <= 0 || experts <= 0 || top <= 0 || top > experts)
             throw ConfigError("routed_mlp: sizes must be positive and top at most the number of experts");
         if (act < 0) throw ConfigError("routed_mlp: activation '" + s.get_string("activation", "silu") + "' is not supported (silu, relu, gelu_tanh)");
-        names = {{"router", "router.weight"}, {"router_bias", "router.bias"}, {"expert", "experts."}, {"gate", "gate_proj.weight"},
+        names = {{"router", "router.weight"}, {"router_bias", "router.bias"}, {"correction", "correction"}, {"expert", "experts."}, {"gate", "gate_proj.weight"},
                  {"up", "up_proj.weight"}, {"down", "down_proj.weight"}};
         if (s.has("names"))
             for (auto& m : s.params.at("names").members()) names[m.first] = m.second.as_string();
@@ -39,17 +74,33 @@ struct RoutedMLP : FeedForward {
     TensorDecls tensors() const override {
         TensorDecls d = {{names.at("router"), TensorDecl{{(long long)experts, hidden}}}};
         if (has_bias) d.push_back({names.at("router_bias"), TensorDecl{{(long long)experts}}});
+        if (has_correction) d.push_back({names.at("correction"), TensorDecl{{(long long)experts}}});
         for (int e = 0; e < experts; e++) {
             d.push_back({expert_tensor(e, "gate"), TensorDecl{{inter, hidden}}});
             d.push_back({expert_tensor(e, "up"), TensorDecl{{inter, hidden}}});
             d.push_back({expert_tensor(e, "down"), TensorDecl{{hidden, inter}}});
         }
+        if (shared)
+            for (auto& t : shared->tensors()) d.push_back({shared_prefix + t.first, t.second});
         return d;
     }
     void load(TensorSource& src) override {
         const size_t es = dtype_size(rt->dtype);
         w_router = fetch_owned(rt, src, names.at("router"), rt->dtype, "a router's matrix");
         if (has_bias) b_router = fetch_owned(rt, src, names.at("router_bias"), DType::F32, "a router's bias");
+        if (has_correction) correction = fetch_owned(rt, src, names.at("correction"), DType::F32, "a router's choice correction");
+        if (shared) {
+            struct Below : TensorSource {
+                TensorSource& src;
+                std::string prefix;
+                Below(TensorSource& s, std::string p) : src(s), prefix(std::move(p)) {}
+                DType kept_dtype(const std::string& n) override { return src.kept_dtype(prefix + n); }
+                void fetch_into(const std::string& n, void* dst, DType want, long long ld) override { src.fetch_into(prefix + n, dst, want, ld); }
+                std::vector<long long> shape(const std::string& n) override { return src.shape(prefix + n); }
+                bool has(const std::string& n) override { return src.has(prefix + n); }
+            } below(src, shared_prefix);
+            shared->load(below);
+        }
         gu_buf = DeviceBuffer(rt->dev, (size_t)experts * 2 * inter * hidden * es, "the experts' packed gate/up matrices");
         down_buf = DeviceBuffer(rt->dev, (size_t)experts * hidden * inter * es, "the experts' down matrices");
         w_gate_up = Mat{gu_buf.get(), (long long)experts * 2 * inter, hidden, rt->dtype, (long long)experts * 2 * inter};
@@ -61,11 +112,22 @@ struct RoutedMLP : FeedForward {
             src.fetch_into(expert_tensor(e, "down"), (char*)w_down.p + (size_t)e * hidden * inter * es, rt->dtype);
         }
     }
-    MatOrPartials forward(const Mat& h, const StepContext&, bool) override {
+    MatOrPartials forward(const Mat& h, const StepContext& ctx, bool) override {
         Device& dev = *rt->dev;
         Mat logits = ops::linear(dev, rt->gemm, h, w_router.m, DType::F32, false).m;
+        ops::MoeRouting route;
+        route.scoring = score_all ? 1 : 0;
+        route.groups = groups;
+        route.keep = keep;
+        route.renorm = score_all ? renorm : true;
+        route.bias = has_bias ? (const float*)b_router.m.p : has_correction ? (const float*)correction.m.p : nullptr;
+        Mat plus;
+        if (shared) {
+            plus = shared->forward(h, ctx, false).m;
+            route.plus = &plus;
+        }
         MatOrPartials r;
-        r.m = ops::moe_forward(dev, h, logits, has_bias ? (const float*)b_router.m.p : nullptr, experts, top, w_gate_up, w_down, act);
+        r.m = ops::moe_forward_ex(dev, h, logits, route, experts, top, w_gate_up, w_down, act);
         return r;
     }
 };

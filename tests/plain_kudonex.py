@@ -1,0 +1,193 @@
+"""A plain, slow implementation of the Kudonex decoder in float64 numpy: one function per mechanism, every
+recurrence and every attention row a literal loop.  It shares nothing with the library; the GPU tests compare the
+engine with it.
+
+A model is (cfg, W): cfg the config.json object, W a dict name -> float64 array.  Everything runs on one
+sequence: x is [n, width], positions count from 0.
+"""
+import math
+
+import numpy as np
+
+
+def sigmoid(z):
+    return 1.0 / (1.0 + np.exp(-z))
+
+
+def silu(z):
+    return z * sigmoid(z)
+
+
+def softplus(z):
+    return np.logaddexp(0.0, z)
+
+
+def log_sigmoid(z):
+    return -np.logaddexp(0.0, -z)
+
+
+def layer_norm(x, w, eps):
+    """(x - mean) / sqrt(var + eps) * w over the last axis, var the mean squared deviation; no bias."""
+    mu = x.mean(-1, keepdims=True)
+    var = ((x - mu) ** 2).mean(-1, keepdims=True)
+    return (x - mu) / np.sqrt(var + eps) * w
+
+
+def rms_unit(x, eps):
+    return x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
+
+
+def causal_conv(h, w, bias=None):
+    """y_t[c] = sum_j w[c, j] * h_(t - taps + 1 + j)[c] (+ bias[c]); rows before the sequence are zero."""
+    n, taps = h.shape[0], w.shape[1]
+    y = np.zeros_like(h)
+    for t in range(n):
+        for j in range(taps):
+            s = t - taps + 1 + j
+            if s >= 0:
+                y[t] += w[:, j] * h[s]
+    if bias is not None:
+        y += bias
+    return y
+
+
+def embed(tokens, table, scale, first_pos=0):
+    """table[token] * scale plus the sinusoid vector: entry 2i sin(p * 10000^(-2i / width)), entry 2i + 1 its cosine."""
+    width = table.shape[1]
+    x = table[np.asarray(tokens)] * scale
+    for r in range(len(tokens)):
+        p = first_pos + r
+        for c in range(width):
+            ang = p * 10000.0 ** (-(2 * (c // 2)) / width)
+            x[r, c] += math.sin(ang) if c % 2 == 0 else math.cos(ang)
+    return x
+
+
+def mlstm_mixer(h, W, pre, m, eps):
+    """The matrix memory with exponential gating and a running maximum that starts at 0."""
+    H, d, dv, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
+    n = h.shape[0]
+    q = (h @ W[pre + "q"].T).reshape(n, H, d) * d ** -0.5
+    k = (h @ W[pre + "k"].T).reshape(n, H, d)
+    v = (h @ W[pre + "v"].T).reshape(n, H, dv)
+    ig = cap * np.tanh((h @ W[pre + "i"].T + W[pre + "i.b"]) / cap)
+    fg = log_sigmoid(cap * np.tanh((h @ W[pre + "f"].T + W[pre + "f.b"]) / cap))
+    out = np.zeros((n, H, dv))
+    for a in range(H):
+        S, nv, mx = np.zeros((d, dv)), np.zeros(d), 0.0
+        for t in range(n):
+            new = max(fg[t, a] + mx, ig[t, a])
+            keep, put = math.exp(fg[t, a] + mx - new), math.exp(ig[t, a] - new)
+            S = keep * S + put * np.outer(k[t, a], v[t, a])
+            nv = keep * nv + put * k[t, a]
+            mx = new
+            out[t, a] = (S.T @ q[t, a]) / (max(abs(nv @ q[t, a]), math.exp(-mx)) + 1e-6)
+    y = rms_unit(out, eps).reshape(n, H * dv) * W[pre + "norm"] * sigmoid(h @ W[pre + "g"].T)
+    return y @ W[pre + "o"].T
+
+
+def mamba2_mixer(h, W, pre, m, eps):
+    """The selective state space in its scalar-decay (duality) form."""
+    H, dv, N, G, parts = m["heads"], m["vdim"], m["state"], m["groups"], m["norm_groups"]
+    n, inner = h.shape[0], m["heads"] * m["vdim"]
+    p = h @ W[pre + "in"].T
+    z, xbc, dt = p[:, :inner], p[:, inner:2 * inner + 2 * G * N], p[:, 2 * inner + 2 * G * N:]
+    xbc = silu(causal_conv(xbc, W[pre + "conv"], W[pre + "conv.b"]))
+    x = xbc[:, :inner].reshape(n, H, dv)
+    Bm = xbc[:, inner:inner + G * N].reshape(n, G, N)
+    Cm = xbc[:, inner + G * N:].reshape(n, G, N)
+    dt = softplus(dt + W[pre + "dt_bias"])
+    y = np.zeros((n, H, dv))
+    for a in range(H):
+        g = a // (H // G)
+        S = np.zeros((N, dv))
+        for t in range(n):
+            S = math.exp(-math.exp(W[pre + "A_log"][a]) * dt[t, a]) * S + dt[t, a] * np.outer(Bm[t, g], x[t, a])
+            y[t, a] = S.T @ Cm[t, g] + W[pre + "D"][a] * x[t, a]
+    y = y.reshape(n, inner) * silu(z)
+    y = rms_unit(y.reshape(n, parts, inner // parts), eps).reshape(n, inner) * W[pre + "norm"]
+    return y @ W[pre + "o"].T
+
+
+def attention_mixer(h, W, pre, m):
+    """Softmax attention over a sliding window whose values are the keys, with a logarithmic distance penalty and the
+    heads' scores mixed by a matrix before the softmax; an element-wise sigmoid gate on the way out."""
+    H, G, d, window, scale = m["heads"], m["kv_heads"], m["dim"], m["mask"]["size"] if m.get("mask") else 0, m["scale"]
+    n = h.shape[0]
+    q = (h @ W[pre + "q"].T).reshape(n, H, d)
+    k = (h @ W[pre + "k"].T).reshape(n, G, d)
+    out = np.zeros((n, H, d))
+    for i in range(n):
+        lo = max(0, i - window + 1) if window else 0
+        js = np.arange(lo, i + 1)
+        s = np.zeros((H, len(js)))
+        for a in range(H):
+            s[a] = (k[js, a // (H // G)] @ q[i, a]) * scale - W[pre + "r1"][a] * np.log1p(W[pre + "r2"][a] * (i - js))
+        s = W[pre + "talk"] @ s
+        for a in range(H):
+            e = np.exp(s[a] - s[a].max())
+            out[i, a] = (e / e.sum()) @ k[js, a // (H // G)]
+    y = out.reshape(n, H * d) * sigmoid(h @ W[pre + "g"].T)
+    return y @ W[pre + "o"].T
+
+
+def expert(h, W, pre):
+    return (silu(h @ W[pre + "gate"].T) * (h @ W[pre + "up"].T)) @ W[pre + "down"].T
+
+
+def route(h, W, pre, r):
+    """Per token: the chosen experts and their weights.  Softmax over all experts; the choice adds a correction and is
+    confined to the best groups (a group's score: its largest corrected score); the weights are the plain scores."""
+    E, top = r["experts"], r["top"]
+    count, keep = (r["groups"]["count"], r["groups"]["keep"]) if r.get("groups") else (1, 1)
+    z = h @ W[pre + "router"].T
+    chosen, weights = [], []
+    for t in range(h.shape[0]):
+        e = np.exp(z[t] - z[t].max())
+        s = e / e.sum()
+        c = s + W[pre + "correction"] if pre + "correction" in W else s.copy()
+        per = E // count
+        gscore = [c[g * per:(g + 1) * per].max() for g in range(count)]
+        kept = sorted(range(count), key=lambda g: (-gscore[g], g))[:keep]
+        allowed = [x for x in range(E) if x // per in kept]
+        pick = sorted(allowed, key=lambda x: (-c[x], x))[:top]
+        chosen.append(pick)
+        weights.append([s[x] for x in pick])
+    return chosen, weights
+
+
+def moe(h, W, pre, mlp):
+    chosen, weights = route(h, W, pre, mlp["router"])
+    y = np.zeros((h.shape[0], W[pre + "e0.down"].shape[0]))
+    for t in range(h.shape[0]):
+        for x, w in zip(chosen[t], weights[t]):
+            y[t] += w * expert(h[t:t + 1], W, pre + "e%d." % x)[0]
+    if mlp.get("shared"):
+        y += expert(h, W, pre + "shared.")
+    return y
+
+
+def forward(cfg, W, tokens, layers_out=None):
+    """Logits [n, vocab] of one sequence from its first token; layers_out (a list) receives the stream after every layer."""
+    eps = cfg["norm"]["eps"]
+    x = embed(tokens, W["embed"], cfg["embedding"]["scale"])
+    for i, L in enumerate(cfg["layers"]):
+        pre = "l%d." % i
+        h = layer_norm(x, W[pre + "norm1"], eps)
+        if cfg.get("canon"):
+            h = h + causal_conv(h, W[pre + "canon1"])
+        if L["type"] == "mlstm":
+            y = mlstm_mixer(h, W, pre + "mix.", L["mixer"], eps)
+        elif L["type"] == "mamba2":
+            y = mamba2_mixer(h, W, pre + "mix.", L["mixer"], eps)
+        elif L["type"] == "attention":
+            y = attention_mixer(h, W, pre + "mix.", L["mixer"])
+        else:
+            raise ValueError(L["type"])
+        x = x + layer_norm(y, W[pre + "norm1b"], eps)
+        if L.get("mlp"):
+            y = moe(layer_norm(x, W[pre + "norm2"], eps), W, pre + "mlp.", L["mlp"])
+            x = x + layer_norm(y, W[pre + "norm2b"], eps)
+        if layers_out is not None:
+            layers_out.append(x.copy())
+    return layer_norm(x, W["final.norm"], eps) @ W["embed"].T
