@@ -191,3 +191,144 @@ def forward(cfg, W, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return layer_norm(x, W["final.norm"], eps) @ W["embed"].T
+
+
+def greedy_generate(cfg, W, prompt, n_new):
+    ids = list(prompt)
+    for _ in range(n_new):
+        ids.append(int(np.argmax(forward(cfg, W, ids)[-1])))
+    return ids[len(prompt):]
+
+
+# ---------------------------------------------------------------- test infrastructure: configurations and weights
+
+
+def random_config(types, width=48, vocab=97, taps=3, emb_scale=2.0, eps=1e-5, heads=2, dim=16, vdim=24, gate_cap=10.0, ssm_heads=4, ssm_vdim=12,
+                  state=16, groups=2, norm_groups=2, conv=3, att_heads=4, kv_heads=2, att_dim=16, window=20, scale=0.5, experts=6, top=2,
+                  group_count=3, group_keep=2, expert_ff=24, shared_ff=40, mlps=None, max_positions=2048):
+    """A small configuration: `types` names the mixers, `mlps` says per layer whether it has a feed-forward (True,
+    "bare": one without groups and without a shared expert, or None); all if not given."""
+    layers = []
+    for i, t in enumerate(types):
+        if t == "mlstm":
+            m = {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": gate_cap}
+        elif t == "mamba2":
+            m = {"heads": ssm_heads, "vdim": ssm_vdim, "state": state, "groups": groups, "norm_groups": norm_groups, "conv": conv}
+        else:
+            m = {"heads": att_heads, "kv_heads": kv_heads, "dim": att_dim, "vdim": att_dim, "scale": scale}
+            if window:
+                m["mask"] = {"size": window}
+        kind = mlps[i] if mlps is not None else True
+        mlp = None
+        if kind:
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+            if kind != "bare":
+                mlp["router"]["groups"] = {"count": group_count, "keep": group_keep}
+                mlp["shared"] = {"ff": shared_ff}
+        layers.append({"type": t, "mixer": m, "mlp": mlp})
+    cfg = {"architecture": "Kudonex", "width": width, "vocab": vocab, "norm": {"eps": eps}, "embedding": {"scale": emb_scale}, "layers": layers,
+           "max_positions": max_positions}
+    if taps:
+        cfg["canon"] = {"taps": taps}
+    return cfg
+
+
+def tensor_shapes(cfg):
+    """name -> (shape, kind); kind says how random_weights draws the tensor."""
+    width, out = cfg["width"], {"embed": ((cfg["vocab"], cfg["width"]), "embed"), "final.norm": ((cfg["width"],), "norm")}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, L["mixer"]
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if L.get("mlp") else ()):
+            out[p + n] = ((width,), "norm")
+        if cfg.get("canon"):
+            out[p + "canon1"] = ((width, cfg["canon"]["taps"]), "taps")
+        x = p + "mix."
+        if L["type"] == "mlstm":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            out.update({x + "q": ((H * d, width), "mat"), x + "k": ((H * d, width), "mat"), x + "v": ((H * dv, width), "mat"),
+                        x + "g": ((H * dv, width), "mat"), x + "o": ((width, H * dv), "mat"), x + "norm": ((H * dv,), "norm"),
+                        x + "i": ((H, width), "mat"), x + "i.b": ((H,), "bias"), x + "f": ((H, width), "mat"), x + "f.b": ((H,), "fbias")})
+        elif L["type"] == "mamba2":
+            H, dv, N, G, c = m["heads"], m["vdim"], m["state"], m["groups"], m.get("conv", 1)
+            inner, ch = H * dv, H * dv + 2 * G * N
+            out.update({x + "in": ((2 * inner + 2 * G * N + H, width), "mat"), x + "conv": ((ch, c), "taps"), x + "conv.b": ((ch,), "bias"),
+                        x + "dt_bias": ((H,), "bias"), x + "A_log": ((H,), "alog"), x + "D": ((H,), "norm"), x + "norm": ((inner,), "norm"),
+                        x + "o": ((width, inner), "mat")})
+        else:
+            H, G, d = m["heads"], m["kv_heads"], m["dim"]
+            out.update({x + "q": ((H * d, width), "mat"), x + "k": ((G * d, width), "mat"), x + "g": ((H * d, width), "mat"),
+                        x + "o": ((width, H * d), "mat"), x + "r1": ((H,), "r1"), x + "r2": ((H,), "r2"), x + "talk": ((H, H), "talk")})
+        if L.get("mlp"):
+            f, r = p + "mlp.", L["mlp"]["router"]
+            out[f + "router"] = ((r["experts"], width), "router")
+            out[f + "correction"] = ((r["experts"],), "correction")
+            blocks = [(f + "e%d." % e, L["mlp"]["expert"]["ff"]) for e in range(r["experts"])]
+            if L["mlp"].get("shared"):
+                blocks.append((f + "shared.", L["mlp"]["shared"]["ff"]))
+            for b, ff in blocks:
+                out.update({b + "gate": ((ff, width), "mat"), b + "up": ((ff, width), "mat"), b + "down": ((width, ff), "mat")})
+    return out
+
+
+def bf16_round(a):
+    """float32 array rounded to the nearest bfloat16 value (ties to even), still float32."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32).reshape(np.shape(a))
+
+
+def random_weights(cfg, seed, gain=1.0):
+    """Random weights, rounded to bfloat16 values.  Drawn so that faults show: router logits are spread (a wrong expert
+    changes the row), corrections have both signs and are large enough to change the choice, decay rates run from slow
+    to fast, the distance factors and the head mix are far from 0 and the identity."""
+    rng, w = np.random.default_rng(seed), {}
+    for name, (shape, kind) in tensor_shapes(cfg).items():
+        n_in = shape[-1]
+        if kind == "mat":
+            a = rng.standard_normal(shape) * gain / math.sqrt(n_in)
+        elif kind == "embed":
+            a = rng.standard_normal(shape)
+        elif kind == "norm":
+            a = 1.0 + 0.3 * rng.standard_normal(shape)
+        elif kind == "taps":
+            a = 0.5 * rng.standard_normal(shape)
+        elif kind == "bias":
+            a = 0.5 * rng.standard_normal(shape)
+        elif kind == "fbias":
+            a = 2.0 + rng.standard_normal(shape)
+        elif kind == "alog":
+            a = np.linspace(-4.0, 0.5, shape[0])
+        elif kind == "r1":
+            a = 0.3 + rng.random(shape)
+        elif kind == "r2":
+            a = 0.2 + 2.0 * rng.random(shape)
+        elif kind == "talk":
+            a = np.eye(shape[0]) + 0.4 * rng.standard_normal(shape)
+        elif kind == "router":
+            a = rng.standard_normal(shape) * 6.0 / math.sqrt(n_in)
+        elif kind == "correction":
+            a = 0.15 * rng.standard_normal(shape)
+        else:
+            raise ValueError(kind)
+        w[name] = bf16_round(a.astype(np.float32))
+    return w
+
+
+def write_model(folder, cfg, w):
+    """config.json and model.safetensors (bfloat16) of (cfg, w) in `folder`."""
+    import json
+    import os
+    import struct
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    header, blobs, off = {}, [], 0
+    for name, a in w.items():
+        blob = (np.ascontiguousarray(a, np.float32).view(np.uint32) >> 16).astype("<u2").tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(np.shape(a)), "data_offsets": [off, off + len(blob)]}
+        blobs.append(blob)
+        off += len(blob)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
