@@ -197,6 +197,25 @@ def vizosun_config(z, vocab=32000, max_positions=4096):
                 embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)), loop=dict(start=1, stop=3, times=2))
 
 
+KUDONEX_LAYERS = ("mlstm", "mamba2", "attention", "mlstm", "mamba2", "attention")
+
+
+def kudonex_config(z, vocab=32000, max_positions=4096):
+    """Six layers of the Kudonex design at the size z: matrix-memory and state-space layers with the linear layers' head
+    count and 128 x 128 state per head (the state-space layers with four taps and a group of B and C per eight heads),
+    attention with a window of 1,024 whose keys are the values, three taps of input convolution in every layer, and
+    in every layer a routed feed-forward of 8 experts in 4 groups (2 kept) of a quarter of the size's feed-forward
+    width, of which a token uses 2, beside a shared expert of half that width (the same active matrix elements as a
+    dense feed-forward of the size)."""
+    H, d = z["lin_heads"], z["lin_d"]
+    mlp = dict(kind="moe", expert=dict(ff=z["ff"] // 4), router=dict(experts=8, top=2, groups=dict(count=4, keep=2)), shared=dict(ff=z["ff"] // 2))
+    mixers = dict(mlstm=dict(heads=H, dim=d, vdim=d, gate_cap=15.0),
+                  mamba2=dict(heads=H, vdim=d, state=d, groups=max(1, H // 8), norm_groups=max(1, H // 8), conv=4),
+                  attention=dict(heads=z["heads"], kv_heads=z["kv"], dim=z["d"], vdim=z["d"], scale=z["d"] ** -0.5, mask=dict(size=1024)))
+    return dict(architecture="Kudonex", layers=[dict(type=t, mixer=dict(mixers[t]), mlp=mlp) for t in KUDONEX_LAYERS], norm=dict(eps=1e-5),
+                vocab=vocab, width=z["width"], max_positions=max_positions, canon=dict(taps=3), embedding=dict(scale=1.0))
+
+
 def llama_twin(z, vocab=32000, max_positions=4096):
     return dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=len(DESIGN_LAYERS),
                 num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["d"], intermediate_size=z["ff"],
@@ -246,6 +265,8 @@ def run_design(args):
         arms = (("vokelix", vokelix_config(z)), ("llama", llama_twin(z)))
         if args.design == "vizosun":
             arms = (("vizosun", vizosun_config(z)),) + arms
+        if args.design == "kudonex":
+            arms = (("kudonex", kudonex_config(z)), ("vizosun", vizosun_config(z))) + arms
         for which, cfgd in arms:
             eng = Engine.from_config(config_from_dict(cfgd), EngineOptions(dtype="bfloat16", max_tokens=max(B * (C + 64), NP * (T + 64)) + 64,
                                                                            max_seq_len=4096, max_batch=max(B, NP, 8)), seed=0)
@@ -275,7 +296,7 @@ def run_design(args):
             dec_ms = timed(one, K)
             for s in slots:
                 eng.end_sequence(s)
-            print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else ["/".join(x) for x in VIZOSUN_LAYERS] if which == "vizosun" else len(DESIGN_LAYERS),
+            print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else ["/".join(x) for x in VIZOSUN_LAYERS] if which == "vizosun" else list(KUDONEX_LAYERS) if which == "kudonex" else len(DESIGN_LAYERS),
                               "prefill_tokens": T, "prefill_prompts": NP, "prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(NP * T / pf_ms * 1e3, 1),
                               "decode_batch": B, "decode_context": C, "decode_ms": round(dec_ms, 4),
                               "decode_tok_s": round(B / dec_ms * 1e3, 1), "prefill_kernels_us": pf_kernels,
@@ -508,7 +529,7 @@ def main():
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
                     "each (or 'toN': until position N), through the Python entry point; 'config' = the workload of --model "
                     "(8b: 16:64:2048:256, 13b: 32:128:1024:to4096)")
-    ap.add_argument("--design", choices=["vokelix", "vizosun"], help="beside the default workload: prompt and decode throughput of this design "
+    ap.add_argument("--design", choices=["vokelix", "vizosun", "kudonex"], help="beside the default workload: prompt and decode throughput of this design "
                     "at a few layer sizes, each next to LLaMA layers of equal size, with the time per kernel")
     ap.add_argument("--design-size", default="1k,2k,4k", help="with --design: sizes to run (1k, 2k, 4k: the width)")
     ap.add_argument("--design-tokens", type=int, default=2048, help="with --design: tokens of the prompt")

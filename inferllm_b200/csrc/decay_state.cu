@@ -62,6 +62,7 @@ struct DecayScanArgs {
     const float *ga, *gb;           // [T, nh]
     int qk_div;                     // value head h reads query/key head h / qk_div (1: a head of its own)
     long long state_stride;         // floats from one slot's state to the next (nh * d * dv unless more is kept beside S)
+    float* seg_gate;                // [B, segments, nh]: the product of a segment's gates a_t (GATED with segments)
 };
 
 __device__ __forceinline__ float act_of(float v, int act) {
@@ -126,7 +127,10 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 //
 // GATED: the decay is not one number per head but a gate per token and head, a_t, and the token's outer product
 // enters with a second one, b_t: S_t = a_t S_(t-1) + b_t k_t v_t^T.  The two gates of a token travel with its staged
-// row.  Value head h may share the queries and keys of head h / qk_div.  Such a step always runs in order (one segment).
+// row.  Value head h may share the queries and keys of head h / qk_div.  With segments, pass 0 also leaves the product
+// of each segment's gates in seg_gate; pass 1 folds the earlier segments' states with these products
+// (S_in = (..(S_0 G_1 + S_1) G_2 + ..) + S_(seg-1)) and gives token t the product of the gates from its segment's
+// start up to itself in place of a power of the decay.
 template <int R, int C, int LI, int PASS, bool GATED>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a) {
     pdl_grid_sync();
@@ -200,7 +204,8 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     };
     float* seg_base = a.seg_state + ((size_t)b * P * a.nh + h) * (size_t)d * dv;      // + seg * nh * d * dv per segment
     const size_t seg_stride = (size_t)a.nh * d * dv;
-    float factor = dec;             // pass 1: decay^(t - t0 + 1) of the token at hand
+    float factor = dec;             // pass 1: decay^(t - t0 + 1) of the token at hand (GATED: the product of the gates up to it)
+    float* seg_gate = GATED && P > 1 ? a.seg_gate + (size_t)b * P * a.nh + h : nullptr;      // + seg * nh per segment
     if (PASS == 0) {
         if (seg == 0) {
             load_state(Sg, 0.f, false);
@@ -220,9 +225,9 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
             }
             return;
         }
-        const float dec_len = power(seg_len);
+        const float dec_len = GATED ? 1.f : power(seg_len);
         load_state(seg_base, 0.f, false);
-        for (int r = 1; r < seg; r++) load_state(seg_base + r * seg_stride, dec_len, true);
+        for (int r = 1; r < seg; r++) load_state(seg_base + r * seg_stride, GATED ? seg_gate[(size_t)r * a.nh] : dec_len, true);
     }
     // rows beyond d and columns beyond dv stay zero in both buffers
     for (int idx = threadIdx.x; idx < 2 * a.tile * ROW; idx += DS_THREADS) sm[idx] = 0.f;
@@ -297,6 +302,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
             float v[C];
             const float dec_t = GATED ? rowp[u * ROW + GATE_AT] : dec;
             const float put_t = GATED ? rowp[u * ROW + GATE_AT + 1] : 1.f;
+            if (GATED && PASS == 0) factor *= dec_t;
 #pragma unroll
             for (int c = 0; c < C; c++) {
                 v[c] = GATED ? vp[c] * put_t : vp[c];
@@ -351,6 +357,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
         // lanes that differ only in the bits of the plain steps hold the same sum: one of them writes
 #pragma unroll
         for (int u = 0; u < U; u++) {
+            if (GATED && PASS == 1) factor *= rowp[u * ROW + GATE_AT];
             if ((lane & plain_bits) == 0) {
                 float* orow = a.out + (size_t)(t + u) * a.nh * dv + (size_t)h * dv + j0 + jl + first;
 #pragma unroll
@@ -360,7 +367,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
                         else orow[c] += factor * p[u][c];
                     }
             }
-            if (PASS == 1) factor *= dec;
+            if (PASS == 1 && !GATED) factor *= dec;
         }
     };
     if (t0 < t1) stage(0, t0);
@@ -385,9 +392,10 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     }
     if (PASS == 0) {
         store_state(P > 1 ? seg_base + seg * seg_stride : Sg);
+        if (GATED && P > 1 && threadIdx.x == 0 && blockIdx.z == 0) seg_gate[(size_t)seg * a.nh] = factor;
     } else if (last_seg) {
         // the sequence's state: what came in, decayed over this segment, plus what the segment added
-        load_state(seg_base + seg * seg_stride, power(t1 - t0), true);
+        load_state(seg_base + seg * seg_stride, GATED ? factor : power(t1 - t0), true);
         store_state(Sg);
     }
 }
@@ -403,11 +411,11 @@ static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {
     const size_t smem = (size_t)2 * a.tile * ROW * sizeof(float);
     if (smem > 48 * 1024) {
         cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 0, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (!GATED) cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 1, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
     const dim3 grid(B * a.segments, a.nh, (a.dv + JB - 1) / JB);
     illm_launch(decay_scan_kernel<R, C, LI, 0, GATED>, grid, dim3(DS_THREADS), smem, s, a);
-    if (!GATED && a.segments > 1) illm_launch(decay_scan_kernel<R, C, LI, 1, false>, grid, dim3(DS_THREADS), smem, s, a);
+    if (a.segments > 1) illm_launch(decay_scan_kernel<R, C, LI, 1, GATED>, grid, dim3(DS_THREADS), smem, s, a);
 }
 
 template <bool GATED>
@@ -436,7 +444,7 @@ extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, in
     if (nh <= 0 || d <= 0 || d > 1024 || dv <= 0 || nh > 65535 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !state || !out)
         return ILLM_ERR_BAD_ARG;
     DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0, 0, segments, seg_state,
-                    nullptr, nullptr, 1, (long long)nh * d * dv};
+                    nullptr, nullptr, 1, (long long)nh * d * dv, nullptr};
     a.vec = !((d | dv | ld | q_off | k_off | v_off) & 3) && !((uintptr_t)x & 15) && !((uintptr_t)state & 15);
     cudaStream_t s = (cudaStream_t)stream;
     // a step of few tokens (single tokens of a batch) is not worth a launch of its own for the preparation
@@ -448,16 +456,17 @@ extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, in
 
 // The same recurrence with a gate pair per token and head (ga, gb: float32 [T, nh]) in place of the fixed decay, the
 // q and k columns read as they are (nqk = nh / qk_div query/key heads).  state: the slots' S [nh, dv, d] blocks,
-// `state_stride` floats apart.
+// `state_stride` floats apart.  segments > 1: seg_state [B, segments, nh, dv, d] and seg_gate [B, segments, nh] are scratch.
 extern "C" int illm_gated_scan(const float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int qk_div, int d, int dv, const float* ga,
                                const float* gb, float* state, long long state_stride, const int* slots, const int* cu_q, float* out, int B,
-                               void* stream) {
+                               int segments, float* seg_state, float* seg_gate, void* stream) {
     if (B <= 0 || T <= 0) return 0;
+    if (segments < 1 || (segments > 1 && (!seg_state || !seg_gate)) || (long long)B * segments > 0x7fffffff) return ILLM_ERR_BAD_ARG;
     if (nh <= 0 || qk_div <= 0 || nh % qk_div || d <= 0 || d > 1024 || dv <= 0 || nh > 65535 || !x || !state || !out || !ga || !gb ||
         state_stride < (long long)nh * d * dv)
         return ILLM_ERR_BAD_ARG;
     DecayScanArgs a{const_cast<float*>(x), ld, q_off, k_off, v_off, nh, d, dv, 0, 0, nullptr, 0, 0, 1.f, nullptr, state, slots, cu_q, nullptr, out, nullptr,
-                    0, 0, 0, 1, nullptr, ga, gb, qk_div, state_stride};
+                    0, 0, 0, segments, seg_state, ga, gb, qk_div, state_stride, seg_gate};
     a.vec = !((d | dv | ld | q_off | k_off | v_off) & 3) && !((uintptr_t)x & 15) && !((uintptr_t)state & 15) && !(state_stride & 3);
     a.inline_prep = 0;
     decay_launch_for<true>(a, B, (cudaStream_t)stream);

@@ -39,7 +39,7 @@ int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc
 // decay_state.cu
 int illm_decay_scan_supported(int d, int dv);
 int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act, const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots, const int* cu_q, const int* token_pos, float* out, int B, int* err, int segments, float* seg_state, void* stream);
-int illm_gated_scan(const float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int qk_div, int d, int dv, const float* ga, const float* gb, float* state, long long state_stride, const int* slots, const int* cu_q, float* out, int B, void* stream);
+int illm_gated_scan(const float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int qk_div, int d, int dv, const float* ga, const float* gb, float* state, long long state_stride, const int* slots, const int* cu_q, float* out, int B, int segments, float* seg_state, float* seg_gate, void* stream);
 int illm_group_norm_gate_ex(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate, int gate_ld, int gate_act, int gate_first, const float* row_scale, int head, const float* skip_w, const float* skip_x, int skip_ld, void* y, int act_dtype, void* stream);
 int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate, int gate_ld, int gate_act, void* y, int act_dtype, void* stream);
 

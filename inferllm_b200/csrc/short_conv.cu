@@ -27,7 +27,8 @@ __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvArgs a) {
     const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= a.C) return;
     const int b = a.token_seq[t], t0 = a.cu_q[b], i = t - t0, n_old = a.taps - 1;
-    const float* st = a.state + (size_t)a.slots[b] * a.state_stride + a.state_off;
+    // one tap keeps no rows: such a call has no state and no slots
+    const float* st = n_old > 0 ? a.state + (size_t)a.slots[b] * a.state_stride + a.state_off : nullptr;
     float acc = 0.f;
     for (int j = 0; j < a.taps; j++) {
         const int s = i - n_old + j;
@@ -59,7 +60,7 @@ extern "C" int illm_short_conv(const float* x, int T, int ldx, int x_off, int C,
                                float* state, long long state_stride, long long state_off, const int* slots, const int* cu_q,
                                const int* token_seq, int B, void* out, int out_dtype, int ldo, int o_off, int update_state, void* stream) {
     if (T <= 0 || B <= 0) return 0;
-    if (C <= 0 || taps < 1 || !x || !w || !out || (taps > 1 && !state) || T > 0x7fffffff / 2) return ILLM_ERR_BAD_ARG;
+    if (C <= 0 || taps < 1 || !x || !w || !out || (taps > 1 && (!state || !slots)) || T > 0x7fffffff / 2) return ILLM_ERR_BAD_ARG;
     ShortConvArgs a{x, ldx, x_off, C, taps, w, bias, act, residual, state, state_stride, state_off, slots, cu_q, token_seq, out, ldo, o_off};
     cudaStream_t s = (cudaStream_t)stream;
     const int by = (C + 255) / 256;

@@ -511,8 +511,12 @@ Mat gated_scan(Device& dev, const Mat& x, const GatedScan& p, const StepView& ct
         throw KernelError("gated_scan: the cache entry does not hold float32 state of heads x head size x value size");
     if (!decay_scan_supported(p.head_dim, p.v_head_dim)) throw KernelError("gated_scan: the head size is beyond the kernel (up to 1024)");
     Mat out = new_mat_exact(dev, x.rows, (long long)p.n_heads * p.v_head_dim, DType::F32);
+    const int segments = (p.in_order || ctx.is_decode) ? 1 : decay_scan_segments(ctx.B, p.n_heads, p.v_head_dim, ctx.max_q, dev.n_sms());
+    float* seg_state = segments > 1 ? dev.alloc_n<float>((size_t)ctx.B * segments * p.n_heads * p.head_dim * p.v_head_dim) : nullptr;
+    float* seg_gate = segments > 1 ? dev.alloc_n<float>((size_t)ctx.B * segments * p.n_heads) : nullptr;
     check_kernel(illm_gated_scan((const float*)x.p, (int)x.rows, (int)x.cols, p.q_off, p.k_off, p.v_off, p.n_heads, p.n_heads / p.n_qk_heads, p.head_dim,
-                                 p.v_head_dim, p.ga, p.gb, (float*)st.state, st.elements, st.slots, ctx.cu_q, (float*)out.p, ctx.B, dev.stream()),
+                                 p.v_head_dim, p.ga, p.gb, (float*)st.state, st.elements, st.slots, ctx.cu_q, (float*)out.p, ctx.B, segments, seg_state, seg_gate,
+                                 dev.stream()),
                  "gated_scan");
     return out;
 }

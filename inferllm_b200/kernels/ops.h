@@ -250,11 +250,12 @@ bool decay_scan_supported(int head_dim, int v_head_dim);
 // The same recurrence with a gate pair per token and head in place of the fixed decay: S_t = a_t S_(t-1) + b_t k_t v_t^T,
 // o_t = S_t^T q_t; ga, gb float32 [T, n_heads] on the device; n_qk_heads query/key heads shared by n_heads / n_qk_heads
 // value heads each; q, k, v are columns of x_f32 and read as they are.  The state block S [n_heads, dv, d] stands at
-// the start of the slot's elements (the entry may hold more behind it).  Always in order.
+// the start of the slot's elements (the entry may hold more behind it).  in_order as in DecayScan.
 struct GatedScan {
     int q_off = 0, k_off = 0, v_off = 0;
     int n_heads = 0, n_qk_heads = 0, head_dim = 0, v_head_dim = 0;
     const float *ga = nullptr, *gb = nullptr;
+    bool in_order = true;
 };
 Mat gated_scan(Device& dev, const Mat& x_f32, const GatedScan& p, const StepView& ctx, const StateView& st);
 // The gates of the matrix memory with exponential gating (csrc/gated_state.cu): from the input and forget logits at

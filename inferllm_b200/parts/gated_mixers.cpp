@@ -127,6 +127,7 @@ struct MatrixMemory : Mixer {
         sp.v_head_dim = v_head_dim;
         sp.ga = ga;
         sp.gb = gb;
+        sp.in_order = rt->is_f32();     // the float32 mode gives the same bits however a prompt is cut
         Mat o = ops::gated_scan(dev, x, sp, ctx, cache.st);
         ops::NormGateExtras ex;
         ex.row_scale = sc;
@@ -212,6 +213,7 @@ struct ScalarDecaySSM : Mixer {
         sp.v_head_dim = v_head_dim;
         sp.ga = ga;
         sp.gb = gb;
+        sp.in_order = rt->is_f32();     // the float32 mode gives the same bits however a prompt is cut
         Mat o = ops::gated_scan(dev, xbc, sp, ctx, cache.st);
         ops::NormGateExtras ex;
         ex.head = v_head_dim;
