@@ -135,9 +135,11 @@ def expert(h, W, pre):
     return (silu(h @ W[pre + "gate"].T) * (h @ W[pre + "up"].T)) @ W[pre + "down"].T
 
 
-def route(h, W, pre, r):
+def route(h, W, pre, r, margins=None):
     """Per token: the chosen experts and their weights.  Softmax over all experts; the choice adds a correction and is
-    confined to the best groups (a group's score: its largest corrected score); the weights are the plain scores."""
+    confined to the best groups (a group's score: its largest corrected score); the weights are the plain scores.
+    `margins` (a list) receives per token how far the choice is from another one: the smaller of the gap between the
+    last kept and the first dropped group and the gap between the last chosen and the first unchosen allowed expert."""
     E, top = r["experts"], r["top"]
     count, keep = (r["groups"]["count"], r["groups"]["keep"]) if r.get("groups") else (1, 1)
     z = h @ W[pre + "router"].T
@@ -150,14 +152,20 @@ def route(h, W, pre, r):
         gscore = [c[g * per:(g + 1) * per].max() for g in range(count)]
         kept = sorted(range(count), key=lambda g: (-gscore[g], g))[:keep]
         allowed = [x for x in range(E) if x // per in kept]
-        pick = sorted(allowed, key=lambda x: (-c[x], x))[:top]
+        ranked = sorted(allowed, key=lambda x: (-c[x], x))
+        pick = ranked[:top]
         chosen.append(pick)
         weights.append([s[x] for x in pick])
+        if margins is not None:
+            by_group = sorted(gscore, reverse=True)
+            gap_g = by_group[keep - 1] - by_group[keep] if keep < count else math.inf
+            gap_e = c[ranked[top - 1]] - c[ranked[top]] if top < len(ranked) else math.inf
+            margins.append(min(gap_g, gap_e))
     return chosen, weights
 
 
-def moe(h, W, pre, mlp):
-    chosen, weights = route(h, W, pre, mlp["router"])
+def moe(h, W, pre, mlp, margins=None):
+    chosen, weights = route(h, W, pre, mlp["router"], margins)
     y = np.zeros((h.shape[0], W[pre + "e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for x, w in zip(chosen[t], weights[t]):
@@ -167,8 +175,9 @@ def moe(h, W, pre, mlp):
     return y
 
 
-def forward(cfg, W, tokens, layers_out=None):
-    """Logits [n, vocab] of one sequence from its first token; layers_out (a list) receives the stream after every layer."""
+def forward(cfg, W, tokens, layers_out=None, margins_out=None):
+    """Logits [n, vocab] of one sequence from its first token; layers_out (a list) receives the stream after every layer,
+    margins_out (a list) one list per routed feed-forward with every token's distance from another choice of experts."""
     eps = cfg["norm"]["eps"]
     x = embed(tokens, W["embed"], cfg["embedding"]["scale"])
     for i, L in enumerate(cfg["layers"]):
@@ -186,11 +195,30 @@ def forward(cfg, W, tokens, layers_out=None):
             raise ValueError(L["type"])
         x = x + layer_norm(y, W[pre + "norm1b"], eps)
         if L.get("mlp"):
-            y = moe(layer_norm(x, W[pre + "norm2"], eps), W, pre + "mlp.", L["mlp"])
+            if margins_out is not None:
+                margins_out.append([])
+            y = moe(layer_norm(x, W[pre + "norm2"], eps), W, pre + "mlp.", L["mlp"], margins_out[-1] if margins_out is not None else None)
             x = x + layer_norm(y, W[pre + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.copy())
     return layer_norm(x, W["final.norm"], eps) @ W["embed"].T
+
+
+def choice_margin(cfg, W, tokens):
+    """Per position the smallest distance of any of its routers from another choice of experts (infinite without one)."""
+    m = []
+    forward(cfg, W, tokens, None, m)
+    return np.min(np.asarray(m, np.float64), 0) if m else np.full(len(tokens), math.inf)
+
+
+def amplification(cfg, W, tokens, rel=1e-7):
+    """By how much the model enlarges a small relative change of its embedding table on the way to the logits, per
+    position (1: not at all).  A unit norm or a layer norm over a vector that happens to be tiny (the matrix memory's
+    read-out at a first token whose query and key are nearly orthogonal, say) enlarges every rounding before it."""
+    ref = forward(cfg, W, tokens)
+    W2 = dict(W)
+    W2["embed"] = W["embed"] * (1.0 + rel * np.random.default_rng(0).standard_normal(W["embed"].shape))
+    return np.abs(forward(cfg, W2, tokens) - ref).max(-1) / np.abs(ref).max() / rel
 
 
 def greedy_generate(cfg, W, prompt, n_new):
