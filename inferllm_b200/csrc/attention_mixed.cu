@@ -29,6 +29,8 @@ struct AttnMixedArgs {
     const float *r1, *r2, *mix, *gate;
     int gate_stride;
     void* out;
+    int splits;         // > 1: block (t, s) takes the s-th part of the token's keys and leaves (acc, m, l) in `part`
+    float* part;        // [T, splits, nh * d + 2 * nh]
 };
 
 template <typename TA>
@@ -62,8 +64,14 @@ __global__ void __launch_bounds__(AM_THREADS) attention_mixed_kernel(AttnMixedAr
     for (int i = 0; i < AM_MAX_ACC; i++) acc[i] = 0.f;
     const bool vec = (d & 7) == 0;
     const int kv_elems = nkv * d;
-    for (int kb = lo; kb <= p; kb += KT) {
-        const int cnt = p - kb + 1 < KT ? p - kb + 1 : KT;
+    int k_lo = lo, k_hi = p;
+    if (a.splits > 1) {     // whole tiles per part, counted from the first visible key
+        const int per = ((p - lo + a.splits) / a.splits + KT - 1) / KT * KT;
+        k_lo = lo + (int)blockIdx.y * per;
+        k_hi = k_lo + per - 1 < p ? k_lo + per - 1 : p;
+    }
+    for (int kb = k_lo; kb <= k_hi; kb += KT) {
+        const int cnt = k_hi - kb + 1 < KT ? k_hi - kb + 1 : KT;
         __syncthreads();        // the tile before this one has been used up (and qs, m, l are written)
         // the tile's key rows, all kv heads of a position side by side
         if (vec) {
@@ -159,6 +167,19 @@ __global__ void __launch_bounds__(AM_THREADS) attention_mixed_kernel(AttnMixedAr
         }
     }
     __syncthreads();
+    if (a.splits > 1) {
+        float* ps = a.part + ((size_t)t * a.splits + blockIdx.y) * (nq + 2 * nh);
+#pragma unroll
+        for (int i = 0; i < AM_MAX_ACC; i++) {
+            const int e = tid + i * AM_THREADS;
+            if (e < nq) ps[e] = acc[i];
+        }
+        for (int h = tid; h < nh; h += AM_THREADS) {
+            ps[nq + h] = m_s[h];
+            ps[nq + nh + h] = l_s[h];
+        }
+        return;
+    }
     TA* o = (TA*)a.out + (size_t)t * nq;
 #pragma unroll
     for (int i = 0; i < AM_MAX_ACC; i++) {
@@ -168,6 +189,30 @@ __global__ void __launch_bounds__(AM_THREADS) attention_mixed_kernel(AttnMixedAr
             if (a.gate) v *= 1.0f / (1.0f + expf(-a.gate[(size_t)t * a.gate_stride + e]));
             o[e] = from_f32<TA>(v);
         }
+    }
+}
+
+// The parts of a token's keys put together: weights exp(m_s - max m), the parts in their order; then the gate.
+template <typename TA>
+__global__ void __launch_bounds__(AM_THREADS) attention_mixed_merge_kernel(AttnMixedArgs a) {
+    pdl_grid_sync();
+    const int t = blockIdx.x, nq = a.nh * a.d, stride = nq + 2 * a.nh;
+    const float* ps = a.part + (size_t)t * a.splits * stride;
+    for (int e = threadIdx.x; e < nq; e += AM_THREADS) {
+        const int h = e / a.d;
+        float mx = -INFINITY;
+        for (int s = 0; s < a.splits; s++) mx = fmaxf(mx, ps[(size_t)s * stride + nq + h]);
+        float l = 0.f, v = 0.f;
+        for (int s = 0; s < a.splits; s++) {
+            const float ms = ps[(size_t)s * stride + nq + h];
+            if (ms == -INFINITY) continue;      // a part without keys
+            const float w = expf(ms - mx);
+            l = fmaf(ps[(size_t)s * stride + nq + a.nh + h], w, l);
+            v = fmaf(ps[(size_t)s * stride + e], w, v);
+        }
+        v /= l;
+        if (a.gate) v *= 1.0f / (1.0f + expf(-a.gate[(size_t)t * a.gate_stride + e]));
+        ((TA*)a.out)[(size_t)t * nq + e] = from_f32<TA>(v);
     }
 }
 
@@ -195,27 +240,38 @@ extern "C" int illm_attention_mixed_supported(int nh, int nkv, int d, int esize)
 }
 
 // q [T, q_stride] and out [T, nh * d] in the activation dtype, kc the keys-only pages; r1, r2 [nh], mix [nh, nh],
-// gate [T, gate_stride] float32, each nullptr to leave its term out.
+// gate [T, gate_stride] float32, each nullptr to leave its term out.  splits > 1 (few tokens over many keys: the
+// blocks of single-token steps would leave most of the GPU idle): every token's keys in that many parts, a block
+// each, over `part` (float32 [T, splits, nh * d + 2 * nh]), and a second kernel that puts the parts together.  The
+// sums then have another order than with one part.
+extern "C" int illm_attention_mixed_keys_per_tile(int nh, int nkv, int d, int esize, int has_mix) {
+    size_t smem;
+    int re;
+    return am_plan(nh, nkv, d, esize, has_mix, &smem, &re);
+}
+
 extern "C" int illm_attention_mixed(const void* q, int q_stride, const void* kc, const int* block_table, int max_pages, const int* token_pos,
                                     const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int page_size, int window,
                                     float scale, const float* r1, const float* r2, const float* mix, const float* gate, int gate_stride,
-                                    void* stream) {
+                                    int splits, float* part, void* stream) {
     if (T <= 0) return 0;
     const int esize = act_dtype == ILLM_F32 ? 4 : 2;
     if ((act_dtype != ILLM_F32 && act_dtype != ILLM_BF16) || !illm_attention_mixed_supported(nh, nkv, d, esize) || !q || !kc || !out ||
-        ((r1 == nullptr) != (r2 == nullptr)) || page_size <= 0)
+        ((r1 == nullptr) != (r2 == nullptr)) || page_size <= 0 || splits < 1 || splits > 65535 || (splits > 1 && !part))
         return ILLM_ERR_BAD_ARG;
     AttnMixedArgs a{q, q_stride, kc, block_table, token_pos, token_seq, max_pages, page_size, window, nh, nkv, d, 0, 0, scale, r1, r2, mix, gate,
-                    gate_stride, out};
+                    gate_stride, out, splits, part};
     size_t smem;
     a.kt = am_plan(nh, nkv, d, esize, mix != nullptr, &smem, &a.row_elems);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == ILLM_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mixed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        illm_launch(attention_mixed_kernel<bf16>, dim3(T), dim3(AM_THREADS), smem, s, a);
+        illm_launch(attention_mixed_kernel<bf16>, dim3(T, splits), dim3(AM_THREADS), smem, s, a);
+        if (splits > 1) illm_launch(attention_mixed_merge_kernel<bf16>, dim3(T), dim3(AM_THREADS), 0, s, a);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mixed_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        illm_launch(attention_mixed_kernel<float>, dim3(T), dim3(AM_THREADS), smem, s, a);
+        illm_launch(attention_mixed_kernel<float>, dim3(T, splits), dim3(AM_THREADS), smem, s, a);
+        if (splits > 1) illm_launch(attention_mixed_merge_kernel<float>, dim3(T), dim3(AM_THREADS), 0, s, a);
     }
     return illm_launch_status();
 }

@@ -10,7 +10,7 @@
 //   m_t = max(f_t + m_(t-1), i_t),  a_t = exp(f_t + m_(t-1) - m_t),  b_t = exp(i_t - m_t)
 //   n_t = a_t n_(t-1) + b_t k_t,  scale_t = q_scale / (max(|q_scale n_t . q_t|, exp(-m_t)) + 1e-6)
 // so that the layer's output is scale_t * S_t^T q_t with the raw q.  m and n are a chain over the sequence's tokens:
-// a warp owns one (sequence, head), keeps n over its lanes, and goes through the tokens in order; the two gates
+// a block owns one (sequence, head), keeps n over its threads, and goes through the tokens in order; the two gates
 // (the tanh, the logarithm) are made for 32 tokens at a time, a token per lane, outside the chain.  n [heads, d] and
 // m [heads] live in the sequence's state at n_off and m_off.
 //
@@ -33,55 +33,79 @@ struct MlstmGateArgs {
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-template <int NR>
-__global__ void __launch_bounds__(128) mlstm_gates_kernel(MlstmGateArgs a) {
+#define MG_G 16          // tokens whose k and q rows a warp asks for together
+
+// A block owns one (sequence, head); warp w owns channels [32 w, 32 w + 32) of n, a channel per lane, so a head of d
+// channels takes ceil(d / 32) warps and every warp has MG_G tokens' rows on their way at a time (nothing of them hangs
+// on the chain: the chain itself is one multiply-add per token).  Every warp runs the chain of m by itself (the same
+// bits in all of them).  A token's n . q is a tree of shuffles inside each warp and then the warps' parts in the order
+// of the warps, added by the first warp once per 32 tokens, a token per lane.
+__global__ void __launch_bounds__(1024) mlstm_gates_kernel(MlstmGateArgs a) {
     pdl_grid_sync();
-    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (unit >= a.B * a.nh) return;
+    __shared__ float part[32][33];       // [token of the block of 32][warp]
+    __shared__ float ga_s[32], gb_s[32], em_s[32];
+    const int unit = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int b = unit / a.nh, h = unit - b * a.nh;
     const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
     float* st = a.state + (size_t)a.slots[b] * a.state_stride;
-    float n[NR];
-#pragma unroll
-    for (int r = 0; r < NR; r++) n[r] = r * 32 + lane < a.d ? st[a.n_off + (size_t)h * a.d + r * 32 + lane] : 0.f;
+    const int c = w * 32 + lane;
+    const bool has = c < a.d;
+    float n = has ? st[a.n_off + (size_t)h * a.d + c] : 0.f;
     float m = st[a.m_off + h];
     const float bi = a.i_bias ? a.i_bias[h] : 0.f, bf = a.f_bias ? a.f_bias[h] : 0.f;
+    const float* kcol = a.x + a.k_off + h * a.d + (has ? c : 0);
+    const float* qcol = a.x + a.q_off + h * a.d + (has ? c : 0);
     for (int tb = t0; tb < t1; tb += 32) {
         const int cnt = t1 - tb < 32 ? t1 - tb : 32;
-        float ig_l = 0.f, fg_l = 0.f;
+        // places beyond the step's last token get gates that leave m and n as they are (f = 0, i = -inf: a = 1,
+        // b = 0), so that the links of the chain need no branch and the compiler can overlap them
+        float ig_l = -INFINITY, fg_l = 0.f;
         if (lane < cnt) {
             const float* row = a.x + (size_t)(tb + lane) * a.ld;
             ig_l = a.cap * tanhf((row[a.i_off + h] + bi) / a.cap);
             fg_l = log_sigmoid_f(a.cap * tanhf((row[a.f_off + h] + bf) / a.cap));
         }
-        for (int j = 0; j < cnt; j++) {
-            const float ig = __shfl_sync(0xffffffffu, ig_l, j), fg = __shfl_sync(0xffffffffu, fg_l, j);
-            const float* row = a.x + (size_t)(tb + j) * a.ld;
-            const float m_new = fmaxf(fg + m, ig);
-            const float ga = expf(fg + m - m_new), gb = expf(ig - m_new);
-            float dot = 0.f;
+        for (int j0 = 0; j0 < cnt; j0 += MG_G) {
+            float kk[MG_G], qq[MG_G];
 #pragma unroll
-            for (int r = 0; r < NR; r++) {
-                const int c = r * 32 + lane;
-                if (c < a.d) {
-                    n[r] = fmaf(ga, n[r], gb * row[a.k_off + h * a.d + c]);
-                    dot = fmaf(n[r], row[a.q_off + h * a.d + c], dot);
+            for (int g = 0; g < MG_G; g++) {
+                const size_t r = (size_t)(tb + (j0 + g < cnt ? j0 + g : cnt - 1)) * a.ld;
+                kk[g] = has ? kcol[r] : 0.f;
+                qq[g] = has ? qcol[r] : 0.f;
+            }
+#pragma unroll
+            for (int g = 0; g < MG_G; g++) {
+                const int j = j0 + g;       // < 32: MG_G divides 32
+                const float ig = __shfl_sync(0xffffffffu, ig_l, j), fg = __shfl_sync(0xffffffffu, fg_l, j);
+                const float m_new = fmaxf(fg + m, ig);
+                const float ga = expf(fg + m - m_new), gb = expf(ig - m_new);
+                n = fmaf(ga, n, gb * kk[g]);
+                const float dot = warp_sum(n * qq[g]);
+                m = m_new;
+                if (lane == 0) {
+                    part[j][w] = dot;
+                    if (w == 0) {
+                        ga_s[j] = ga;
+                        gb_s[j] = gb;
+                        em_s[j] = expf(-m_new);
+                    }
                 }
             }
-            dot = warp_sum(dot) * a.q_scale;
-            m = m_new;
-            if (lane == 0) {
-                const size_t o = (size_t)(tb + j) * a.nh + h;
-                a.ga[o] = ga;
-                a.gb[o] = gb;
-                a.scale[o] = a.q_scale / (fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f);
-            }
         }
+        __syncthreads();
+        if (w == 0 && lane < cnt) {
+            float dot = 0.f;
+            for (int i = 0; i < nw; i++) dot += part[lane][i];
+            dot *= a.q_scale;
+            const size_t o = (size_t)(tb + lane) * a.nh + h;
+            a.ga[o] = ga_s[lane];
+            a.gb[o] = gb_s[lane];
+            a.scale[o] = a.q_scale / (fmaxf(fabsf(dot), em_s[lane]) + 1e-6f);
+        }
+        __syncthreads();
     }
-#pragma unroll
-    for (int r = 0; r < NR; r++)
-        if (r * 32 + lane < a.d) st[a.n_off + (size_t)h * a.d + r * 32 + lane] = n[r];
-    if (lane == 0) st[a.m_off + h] = m;
+    if (has) st[a.n_off + (size_t)h * a.d + c] = n;
+    if (threadIdx.x == 0) st[a.m_off + h] = m;
 }
 
 extern "C" int illm_mlstm_gates(const float* x, int T, int ld, int q_off, int k_off, int i_off, int f_off, const float* i_bias, const float* f_bias,
@@ -90,14 +114,7 @@ extern "C" int illm_mlstm_gates(const float* x, int T, int ld, int q_off, int k_
     if (T <= 0 || B <= 0) return 0;
     if (nh <= 0 || d <= 0 || d > 1024 || !(cap > 0.f) || !x || !state || !ga || !gb || !scale) return ILLM_ERR_BAD_ARG;
     MlstmGateArgs a{x, ld, q_off, k_off, i_off, f_off, i_bias, f_bias, cap, q_scale, nh, d, state, state_stride, n_off, m_off, slots, cu_q, ga, gb, scale, B};
-    cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(((unsigned)B * nh + 3) / 4), block(128);
-    if (d <= 32) illm_launch(mlstm_gates_kernel<1>, grid, block, 0, s, a);
-    else if (d <= 64) illm_launch(mlstm_gates_kernel<2>, grid, block, 0, s, a);
-    else if (d <= 128) illm_launch(mlstm_gates_kernel<4>, grid, block, 0, s, a);
-    else if (d <= 256) illm_launch(mlstm_gates_kernel<8>, grid, block, 0, s, a);
-    else if (d <= 512) illm_launch(mlstm_gates_kernel<16>, grid, block, 0, s, a);
-    else illm_launch(mlstm_gates_kernel<32>, grid, block, 0, s, a);
+    illm_launch(mlstm_gates_kernel, dim3((unsigned)B * nh), dim3(32 * ((d + 31) / 32)), 0, (cudaStream_t)stream, a);
     return illm_launch_status();
 }
 

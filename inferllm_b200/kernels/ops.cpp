@@ -560,9 +560,30 @@ Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView&
         throw KernelError("attention_mixed: " + std::to_string(g.n_heads) + " heads of " + std::to_string(g.head_dim) + " channels are beyond the kernel");
     if (q.cols < (long long)g.n_heads * g.head_dim) throw KernelError("attention_mixed: q is narrower than heads x head size");
     Mat out = new_mat(dev, q.rows, (long long)g.n_heads * g.head_dim, q.dtype);
+    // Prompts and their portions in bfloat16: 16 tokens of a sequence per block, the two products on tensor cores.
+    if (q.dtype == DType::BF16 && q.rows > 64 && q.cols % 8 == 0 && (!m.gate || m.gate_stride % 2 == 0) &&
+        illm_attention_mixed_tc_supported(g.n_heads, g.n_kv_heads, g.head_dim)) {
+        check_kernel(illm_attention_mixed_tc(q.p, (int)q.cols, kv.k, kv.block_table, kv.width, ctx.token_pos, ctx.cu_q, ctx.B, out.p, (int)q.rows, g.n_heads,
+                                             g.n_kv_heads, g.head_dim, kv.page_size, kv.window, scale, m.r1, m.r2, m.mix, m.gate, m.gate_stride,
+                                             dev.stream()),
+                     "attention_mixed_tc");
+        return out;
+    }
+    // Few tokens over many keys (single-token steps): the keys in parts, so that the step fills the GPU.  How many
+    // depends on the step's shape and the cache's limits alone, never on a sequence's length, so that a captured
+    // step can be replayed.  The float32 mode keeps one part: its sums have one order for every step.
+    int splits = 1;
+    float* part = nullptr;
+    if (q.dtype != DType::F32 && q.rows <= 64) {
+        const long long span = kv.window > 0 && kv.window < ctx.max_seq_len ? kv.window : ctx.max_seq_len;
+        const int kt = illm_attention_mixed_keys_per_tile(g.n_heads, g.n_kv_heads, g.head_dim, (int)dtype_size(q.dtype), m.mix != nullptr);
+        const long long by_keys = (span + 2 * kt - 1) / (2 * kt), by_blocks = std::max<long long>(1, 2LL * dev.n_sms() / q.rows);
+        splits = (int)std::max<long long>(1, std::min(by_keys, by_blocks));
+        if (splits > 1) part = dev.alloc_n<float>((size_t)q.rows * splits * ((size_t)g.n_heads * g.head_dim + 2 * g.n_heads));
+    }
     check_kernel(illm_attention_mixed(q.p, (int)q.cols, kv.k, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, code_of(q.dtype, "attention_mixed"),
                                       (int)q.rows, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size, kv.window, scale, m.r1, m.r2, m.mix, m.gate,
-                                      m.gate_stride, dev.stream()),
+                                      m.gate_stride, splits, part, dev.stream()),
                  "attention_mixed");
     return out;
 }

@@ -190,6 +190,28 @@ def test_long_prompt_through_the_fused_products(tmp_path, dtype):
     same_or_close(in_portions(eng, ids, [520, 1]), got, dtype, "the same, its last tokens one by one")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv,dim,window", [(12, 4, 128, 37), (4, 4, 64, 0), (3, 1, 32, 16), (20, 2, 16, 17), (2, 1, 48, 90)])
+def test_prompt_attention_in_token_tiles(tmp_path, heads, kv, dim, window, dtype):
+    """Prompts and portions long enough for the kernel that takes 16 tokens of a sequence per block (bfloat16): head
+    counts that one block holds and that take several, windows that end inside a tile of tokens and of keys, tiles
+    that two sequences of a batch share a step with, a last tile of one token, and each alone for comparison."""
+    cfg = pk.random_config((A,), mlps=[None], taps=0, att_heads=heads, kv_heads=kv, att_dim=dim, window=window, scale=dim ** -0.5 * 2, width=64)
+    w = write_model(str(tmp_path), cfg, 17)
+    a, b = prompt(cfg, 161, 4), prompt(cfg, 83, 5)
+    ra, rb = pk.forward(cfg, w, a), pk.forward(cfg, w, b)
+    eng = engine(str(tmp_path), dtype)
+    close(whole(eng, a), ra, dtype, "one prompt")
+    close(in_portions(eng, a, [70, 91]), ra, dtype, "two long portions")
+    close(in_portions(eng, a, [97, 1, 3, 60]), ra, dtype, "portions long and short")
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    lg = eng.step([StepItem(sa, a, list(range(len(a)))), StepItem(sb, b, list(range(len(b))))]).cpu().numpy()
+    eng.end_sequence(sa)
+    eng.end_sequence(sb)
+    close(lg[:len(a)], ra, dtype, "first of two prompts in a step")
+    close(lg[len(a):], rb, dtype, "second of two prompts in a step")
+
+
 # ------------------------------------------------------------------ whole models
 
 
