@@ -8,7 +8,7 @@
 // repeated by the heads / HS blocks of a token tile) and mixes, normalises and weighs only for its own HS heads.
 // Per tile of AT_KT keys, staged once for all key heads:
 //   1. raw_g(i, j) = q_g(i) . k(j) * scale - r1_g ln(1 + r2_g (p_i - j)), a head per warp in turn  -> shared memory
-//   2. a thread per (i, j): s_h = sum_g mix[h, g] raw_g, g ascending, for the block's heads; hidden pairs get -inf
+//   2. two threads per (i, j), half of the block's heads each: s_h = sum_g mix[h, g] raw_g, g ascending, for the block's heads; hidden pairs get -inf
 //   3. a thread per (head, query) row: the running maximum and sum, the tile's weights, the old sums' correction
 //   4. o_h(i) <- o_h(i) corr + P_h K: the weights as two bfloat16 (upper and lower half of 16 bits of mantissa), the
 //      keys read transposed from the staged tile; a warp owns some of the (head, 8 channels) tiles of the output.
@@ -16,10 +16,10 @@
 
 #include "common.cuh"
 
-#define AT_THREADS 256
+#define AT_THREADS 512
 #define AT_BQ 16
 #define AT_KT 16
-#define AT_ACC 16          // (head, 8 channels) output tiles per warp at most: HS * d <= 1024
+#define AT_ACC 8           // (head, 8 channels) output tiles per warp at most: HS * d <= 1024 over 16 warps
 #define AT_LD (AT_KT + 1)  // floats per (head, query) row of scores
 
 struct AttnMixedTcArgs {
@@ -75,6 +75,8 @@ static __host__ __device__ inline AtPlan at_plan(int nh, int nkv, int d, int hs)
     return p;
 }
 
+// HSM: a power of two that is at least the heads per block (the bound of the loops over a pair's heads)
+template <int HSM>
 __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixedTcArgs a) {
     pdl_grid_sync();
     extern __shared__ __align__(16) unsigned char at_raw[];
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
     float acc[AT_ACC][4];
 #pragma unroll
     for (int x = 0; x < AT_ACC; x++) acc[x][0] = acc[x][1] = acc[x][2] = acc[x][3] = 0.f;
-    const int d8 = d >> 3, n_out = HS * d8, per = (n_out + 7) >> 3;     // output tiles, and how many a warp owns
+    const int d8 = d >> 3, n_out = HS * d8, per = (n_out + AT_THREADS / 32 - 1) / (AT_THREADS / 32);     // output tiles, and how many a warp owns
     const int kper8 = (nkv * d) >> 3;
 
     for (int kb = lo_first; kb <= p_last; kb += AT_KT) {
@@ -157,33 +159,37 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
                 float s = ((v & 4) ? c1[v & 3] : c0[v & 3]) * a.scale;
                 if (a.r1) {
                     const int dist = pos_s[i] - (kb + j);
-                    s -= r1 * log1pf(r2 * (float)(dist > 0 ? dist : 0));
+                    s -= r1 * __logf(1.0f + r2 * (float)(dist > 0 ? dist : 0));
                 }
                 raw[(h * AT_BQ + i) * AT_LD + j] = s;
             }
         }
         __syncthreads();
-        // 2. the block's heads' mixed scores, a pair per thread
+        // 2. the block's heads' mixed scores: a pair and half of the block's heads per thread
         {
-            const int i = tid >> 4, j = tid & 15, key = kb + j, pi = pos_s[i];
+            constexpr int HH = HSM > 1 ? HSM / 2 : 1;
+            const int pair = tid & 255, hb = (tid >> 8) * HH;
+            const int i = pair >> 4, j = pair & 15, key = kb + j, pi = pos_s[i];
             const int lo_i = (a.window > 0 && pi - a.window + 1 > 0) ? pi - a.window + 1 : 0;
             const bool visible = pi >= 0 && key <= pi && key >= lo_i;
             const int at = i * AT_LD + j;
             if (a.mix) {
-                float s[16];
+                float s[HH];
 #pragma unroll
-                for (int hh = 0; hh < 16; hh++) s[hh] = 0.f;
+                for (int x = 0; x < HH; x++) s[x] = 0.f;
                 for (int g = 0; g < nh; g++) {
                     const float r = raw[g * AT_BQ * AT_LD + at];
 #pragma unroll
-                    for (int hh = 0; hh < 16; hh++)
-                        if (hh < HS) s[hh] = fmaf(mix_s[hh * nh + g], r, s[hh]);
+                    for (int x = 0; x < HH; x++)
+                        if (hb + x < HS) s[x] = fmaf(mix_s[(hb + x) * nh + g], r, s[x]);
                 }
 #pragma unroll
-                for (int hh = 0; hh < 16; hh++)
-                    if (hh < HS) pr[hh * AT_BQ * AT_LD + at] = visible ? s[hh] : -INFINITY;
+                for (int x = 0; x < HH; x++)
+                    if (hb + x < HS) pr[(hb + x) * AT_BQ * AT_LD + at] = visible ? s[x] : -INFINITY;
             } else {
-                for (int hh = 0; hh < HS; hh++) pr[hh * AT_BQ * AT_LD + at] = visible ? raw[(h0 + hh) * AT_BQ * AT_LD + at] : -INFINITY;
+#pragma unroll
+                for (int x = 0; x < HH; x++)
+                    if (hb + x < HS) pr[(hb + x) * AT_BQ * AT_LD + at] = visible ? raw[(h0 + hb + x) * AT_BQ * AT_LD + at] : -INFINITY;
             }
         }
         __syncthreads();
@@ -199,10 +205,10 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
 #pragma unroll
                 for (int j = 0; j < AT_KT; j++) row[j] = 0.f;
             } else {
-                corr = expf(m_run - m_new);
+                corr = __expf(m_run - m_new);
 #pragma unroll
                 for (int j = 0; j < AT_KT; j++) {
-                    const float w = expf(row[j] - m_new);
+                    const float w = __expf(row[j] - m_new);
                     row[j] = w;
                     sum += w;
                 }
@@ -276,6 +282,12 @@ static int at_heads_per_block(int nh, int d) {
     return 0;
 }
 
+template <int HSM>
+static void at_launch(const AttnMixedTcArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mixed_tc_kernel<HSM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    illm_launch(attention_mixed_tc_kernel<HSM>, grid, dim3(AT_THREADS), smem, s, a);
+}
+
 // bfloat16, head sizes that are multiples of 16 up to 1024, and a token tile's q with a key tile in shared memory
 extern "C" int illm_attention_mixed_tc_supported(int nh, int nkv, int d) {
     if (nh <= 0 || nkv <= 0 || nh % nkv || d <= 0 || d % 16) return 0;
@@ -288,16 +300,25 @@ extern "C" int illm_attention_mixed_tc_supported(int nh, int nkv, int d) {
 // offsets in the step, block_table [B, max_pages]; r1, r2, mix, gate as for illm_attention_mixed.
 extern "C" int illm_attention_mixed_tc(const void* q, int q_stride, const void* kc, const int* block_table, int max_pages, const int* token_pos,
                                        const int* cu_q, int B, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale,
-                                       const float* r1, const float* r2, const float* mix, const float* gate, int gate_stride, void* stream) {
+                                       const float* r1, const float* r2, const float* mix, const float* gate, int gate_stride, int n_sms,
+                                       void* stream) {
     if (T <= 0 || B <= 0) return 0;
     if (!illm_attention_mixed_tc_supported(nh, nkv, d) || !q || !kc || !out || !cu_q || !token_pos || !block_table || q_stride % 8 ||
         ((r1 == nullptr) != (r2 == nullptr)) || page_size <= 0 || (gate && gate_stride % 2))
         return ILLM_ERR_BAD_ARG;
-    const int hs = at_heads_per_block(nh, d);
+    // a short step would leave SMs without a block: fewer heads per block then, as long as the blocks still run all at
+    // once (q k^T is repeated once more per halving)
+    int hs = at_heads_per_block(nh, d);
+    while (hs % 2 == 0 && 2LL * (T / AT_BQ + B) * (nh / hs) <= n_sms) hs /= 2;
     AttnMixedTcArgs a{(const bf16*)q, q_stride, (const bf16*)kc, block_table, token_pos, cu_q, max_pages, page_size, window, nh, nkv, d, hs, B,
                       scale, r1, r2, mix, gate, gate_stride, (bf16*)out};
     const size_t smem = at_plan(nh, nkv, d, hs).total;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mixed_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    illm_launch(attention_mixed_tc_kernel, dim3((unsigned)(T / AT_BQ + B), (unsigned)(nh / hs)), dim3(AT_THREADS), smem, (cudaStream_t)stream, a);
+    const dim3 grid((unsigned)(T / AT_BQ + B), (unsigned)(nh / hs));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hs <= 1) at_launch<1>(a, grid, smem, s);
+    else if (hs <= 2) at_launch<2>(a, grid, smem, s);
+    else if (hs <= 4) at_launch<4>(a, grid, smem, s);
+    else if (hs <= 8) at_launch<8>(a, grid, smem, s);
+    else at_launch<16>(a, grid, smem, s);
     return illm_launch_status();
 }

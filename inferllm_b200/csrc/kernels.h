@@ -32,7 +32,7 @@ int illm_attention_mixed(const void* q, int q_stride, const void* kc, const int*
 int illm_attention_mixed_keys_per_tile(int nh, int nkv, int d, int esize, int has_mix);
 // attention_mixed_tc.cu
 int illm_attention_mixed_tc_supported(int nh, int nkv, int d);
-int illm_attention_mixed_tc(const void* q, int q_stride, const void* kc, const int* block_table, int max_pages, const int* token_pos, const int* cu_q, int B, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, const float* r1, const float* r2, const float* mix, const float* gate, int gate_stride, void* stream);
+int illm_attention_mixed_tc(const void* q, int q_stride, const void* kc, const int* block_table, int max_pages, const int* token_pos, const int* cu_q, int B, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, const float* r1, const float* r2, const float* mix, const float* gate, int gate_stride, int n_sms, void* stream);
 
 // attention_prefill.cu
 int illm_attention_prefill(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, void* stream);

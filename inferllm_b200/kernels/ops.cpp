@@ -565,7 +565,7 @@ Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView&
         illm_attention_mixed_tc_supported(g.n_heads, g.n_kv_heads, g.head_dim)) {
         check_kernel(illm_attention_mixed_tc(q.p, (int)q.cols, kv.k, kv.block_table, kv.width, ctx.token_pos, ctx.cu_q, ctx.B, out.p, (int)q.rows, g.n_heads,
                                              g.n_kv_heads, g.head_dim, kv.page_size, kv.window, scale, m.r1, m.r2, m.mix, m.gate, m.gate_stride,
-                                             dev.stream()),
+                                             dev.n_sms(), dev.stream()),
                      "attention_mixed_tc");
         return out;
     }
