@@ -8,6 +8,7 @@
 // repeated by the heads / HS blocks of a token tile) and mixes, normalises and weighs only for its own HS heads.
 // Per tile of AT_KT keys, staged once for all key heads:
 //   1. raw_g(i, j) = q_g(i) . k(j) * scale - r1_g ln(1 + r2_g (p_i - j)), a head per warp in turn  -> shared memory
+//      (the distance terms from a table of the tile's 31 distances per head)
 //   2. two threads per (i, j), half of the block's heads each: s_h = sum_g mix[h, g] raw_g, g ascending, for the block's heads; hidden pairs get -inf
 //   3. a thread per (head, query) row: the running maximum and sum, the tile's weights, the old sums' correction
 //   4. o_h(i) <- o_h(i) corr + P_h K: the weights as two bfloat16 (upper and lower half of 16 bits of mantissa), the
@@ -55,7 +56,7 @@ __device__ __forceinline__ void at_split(float x, float y, unsigned& hi, unsigne
 
 struct AtPlan {
     int q_ld, k_ld;                                   // elements per staged q row and key row
-    size_t q_off, k_off, raw_off, pr_off, corr_off, l_off, mix_off, pos_off, total;
+    size_t q_off, k_off, raw_off, pr_off, corr_off, l_off, mix_off, pos_off, tab_off, total;
 };
 
 static __host__ __device__ inline AtPlan at_plan(int nh, int nkv, int d, int hs) {
@@ -71,6 +72,7 @@ static __host__ __device__ inline AtPlan at_plan(int nh, int nkv, int d, int hs)
     p.l_off = at, at += (size_t)hs * AT_BQ * 4;
     p.mix_off = at, at += (size_t)hs * nh * 4;
     p.pos_off = at, at += AT_BQ * 4;
+    p.tab_off = at, at += (size_t)nh * 32 * 4;
     p.total = (at + 15) & ~(size_t)15;
     return p;
 }
@@ -90,6 +92,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
     float* l_s = reinterpret_cast<float*>(at_raw + pl.l_off);        // [HS][16]
     float* mix_s = reinterpret_cast<float*>(at_raw + pl.mix_off);    // [HS][nh]: the block's rows of the mix
     int* pos_s = reinterpret_cast<int*>(at_raw + pl.pos_off);        // [16], -1 beyond the sequence's tokens
+    float* tab_s = reinterpret_cast<float*>(at_raw + pl.tab_off);    // [nh][32]: the tile's distance terms
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
     const int q_ld = pl.q_ld, k_ld = pl.k_ld;
 
@@ -140,6 +143,14 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
             }
             *reinterpret_cast<uint4*>(k_s + (size_t)j * k_ld + e) = v;
         }
+        // the distance terms of the tile: a sequence's tokens have consecutive positions, so the pair (i, j) is
+        // p_first + i - kb - j apart, one of 31 distances; entry [h][i - j + 15] (hidden pairs, whose distance is
+        // negative, get the term of distance 0 and are masked later)
+        if (a.r1)
+            for (int idx = tid; idx < nh * 32; idx += AT_THREADS) {
+                const int h = idx >> 5, dist = p_first - kb + (idx & 31) - 15;
+                tab_s[idx] = a.r1[h] * __logf(1.0f + a.r2[h] * (float)(dist > 0 ? dist : 0));
+            }
         __syncthreads();
         // 1. every head's raw scores of the 16 x 16 pairs
         for (int h = warp; h < nh; h += AT_THREADS / 32) {
@@ -152,15 +163,11 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
                 at_mma(c0, a0, a1, a2, a3, *reinterpret_cast<const unsigned*>(ka + k0), *reinterpret_cast<const unsigned*>(ka + k0 + 8));
                 at_mma(c1, a0, a1, a2, a3, *reinterpret_cast<const unsigned*>(ka + 8 * k_ld + k0), *reinterpret_cast<const unsigned*>(ka + 8 * k_ld + k0 + 8));
             }
-            const float r1 = a.r1 ? a.r1[h] : 0.f, r2 = a.r1 ? a.r2[h] : 0.f;
 #pragma unroll
             for (int v = 0; v < 8; v++) {
                 const int i = gid + ((v & 2) ? 8 : 0), j = 2 * tig + (v & 1) + ((v & 4) ? 8 : 0);
                 float s = ((v & 4) ? c1[v & 3] : c0[v & 3]) * a.scale;
-                if (a.r1) {
-                    const int dist = pos_s[i] - (kb + j);
-                    s -= r1 * __logf(1.0f + r2 * (float)(dist > 0 ? dist : 0));
-                }
+                if (a.r1) s -= tab_s[h * 32 + i - j + 15];
                 raw[(h * AT_BQ + i) * AT_LD + j] = s;
             }
         }

@@ -12,7 +12,7 @@
 #include "common.cuh"
 
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 ln_sandwich_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb, const float* __restrict__ w,
                    TO* __restrict__ out, const int* __restrict__ rows, int H, float eps, int write_x) {
     pdl_grid_sync();
@@ -65,12 +65,15 @@ extern "C" int illm_layernorm_sandwich(float* x, const float* y, const float* wb
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
+    // four elements per thread and pass for wide rows: a step of few rows is a few blocks, each bound by the latency of
+    // its passes.  The block's size follows from the width alone, so a row's sums have one order in every step.
+    const dim3 block(H >= 4096 ? 1024 : H >= 2048 ? 512 : 256);
     if (out_dtype == ILLM_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(ln_sandwich_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        illm_launch(ln_sandwich_kernel<bf16>, dim3(n_rows), dim3(256), smem, s, x, y, wb, w, (bf16*)out, rows, H, eps, write_x);
+        illm_launch(ln_sandwich_kernel<bf16>, dim3(n_rows), block, smem, s, x, y, wb, w, (bf16*)out, rows, H, eps, write_x);
     } else if (out_dtype == ILLM_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(ln_sandwich_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        illm_launch(ln_sandwich_kernel<float>, dim3(n_rows), dim3(256), smem, s, x, y, wb, w, (float*)out, rows, H, eps, write_x);
+        illm_launch(ln_sandwich_kernel<float>, dim3(n_rows), block, smem, s, x, y, wb, w, (float*)out, rows, H, eps, write_x);
     } else {
         return ILLM_ERR_BAD_ARG;
     }
