@@ -21,6 +21,7 @@
 #define AT_BQ 16
 #define AT_KT 16
 #define AT_ACC 8           // (head, 8 channels) output tiles per warp at most: HS * d <= 1024 over 16 warps
+#define AT_ST 4           // pieces of 16 bytes of a key tile per thread whose places are kept in registers
 #define AT_LD (AT_KT + 1)  // floats per (head, query) row of scores
 
 struct AttnMixedTcArgs {
@@ -28,7 +29,7 @@ struct AttnMixedTcArgs {
     int q_stride;
     const bf16* kc;
     const int *block_table, *token_pos, *cu_q;
-    int max_pages, page_size, window;
+    int max_pages, page_size, page_shift, window;      // page_shift: log2 of the page size, -1 if it is no power of two
     int nh, nkv, d, hs, B;
     float scale;
     const float *r1, *r2, *mix, *gate;
@@ -131,10 +132,39 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
     for (int x = 0; x < AT_ACC; x++) acc[x][0] = acc[x][1] = acc[x][2] = acc[x][3] = 0.f;
     const int d8 = d >> 3, n_out = HS * d8, per = (n_out + AT_THREADS / 32 - 1) / (AT_THREADS / 32);     // output tiles, and how many a warp owns
     const int kper8 = (nkv * d) >> 3;
+    // which pieces of a key tile this thread stages are the same for every tile: taken apart once (no division in the walk)
+    const size_t page_elems = (size_t)nkv * a.page_size * d;
+    int st_j[AT_ST], st_src[AT_ST], st_dst[AT_ST];
+#pragma unroll
+    for (int r = 0; r < AT_ST; r++) {
+        const int idx = tid + r * AT_THREADS;
+        st_j[r] = -1, st_src[r] = 0, st_dst[r] = 0;
+        if (idx < AT_KT * kper8) {
+            const int j = idx / kper8, e = (idx - j * kper8) << 3, hk = e / d, c = e - hk * d;
+            st_j[r] = j;
+            st_src[r] = hk * a.page_size * d + c;
+            st_dst[r] = j * k_ld + e;
+        }
+    }
+    // the first output tile of this warp; the others follow by counting
+    const int u0 = warp * per, hh_first = u0 / d8, nt_first = u0 - hh_first * d8;
 
     for (int kb = lo_first; kb <= p_last; kb += AT_KT) {
         __syncthreads();        // the tile before this one has been used up
-        for (int idx = tid; idx < AT_KT * kper8; idx += AT_THREADS) {
+#pragma unroll
+        for (int r = 0; r < AT_ST; r++) {
+            if (st_j[r] >= 0) {
+                const int key = kb + st_j[r];
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (key <= p_last) {
+                    const int pg = a.page_shift >= 0 ? key >> a.page_shift : key / a.page_size;
+                    const int in_pg = key - pg * a.page_size;
+                    v = *reinterpret_cast<const uint4*>(a.kc + (size_t)bt[pg] * page_elems + st_src[r] + in_pg * d);
+                }
+                *reinterpret_cast<uint4*>(k_s + st_dst[r]) = v;
+            }
+        }
+        for (int idx = tid + AT_ST * AT_THREADS; idx < AT_KT * kper8; idx += AT_THREADS) {      // key rows beyond AT_ST pieces per thread
             const int j = idx / kper8, e = (idx - j * kper8) << 3, hk = e / d, c = e - hk * d, key = kb + j;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (key <= p_last) {
@@ -230,11 +260,10 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
             int cur = -1;
             unsigned ah[4] = {0u, 0u, 0u, 0u}, al[4] = {0u, 0u, 0u, 0u};
             float cg = 1.f, cg8 = 1.f;
+            int hh = hh_first, nt = nt_first;
 #pragma unroll
             for (int x = 0; x < AT_ACC; x++) {
-                const int u = warp * per + x;
-                if (x < per && u < n_out) {
-                    const int hh = u / d8, nt = u - hh * d8;
+                if (x < per && u0 + x < n_out) {
                     if (hh != cur) {
                         cur = hh;
                         const float* pw = pr + hh * AT_BQ * AT_LD;
@@ -251,6 +280,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
                     at_ldmatrix_x2_trans(b0, b1, (unsigned)__cvta_generic_to_shared(vb));
                     at_mma(acc[x], ah[0], ah[1], ah[2], ah[3], b0, b1);
                     at_mma(acc[x], al[0], al[1], al[2], al[3], b0, b1);
+                    if (++nt == d8) nt = 0, hh++;
                 }
             }
         }
@@ -259,9 +289,8 @@ __global__ void __launch_bounds__(AT_THREADS) attention_mixed_tc_kernel(AttnMixe
     __syncthreads();
 #pragma unroll
     for (int x = 0; x < AT_ACC; x++) {
-        const int u = warp * per + x;
-        if (x < per && u < n_out) {
-            const int hh = u / d8, nt = u - hh * d8;
+        if (x < per && u0 + x < n_out) {
+            const int hh = (u0 + x) / d8, nt = u0 + x - hh * d8;
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 const int i = gid + 8 * half;
@@ -317,7 +346,10 @@ extern "C" int illm_attention_mixed_tc(const void* q, int q_stride, const void* 
     // once (q k^T is repeated once more per halving)
     int hs = at_heads_per_block(nh, d);
     while (hs % 2 == 0 && 2LL * (T / AT_BQ + B) * (nh / hs) <= n_sms) hs /= 2;
-    AttnMixedTcArgs a{(const bf16*)q, q_stride, (const bf16*)kc, block_table, token_pos, cu_q, max_pages, page_size, window, nh, nkv, d, hs, B,
+    int page_shift = -1;
+    for (int b = 0; b < 31; b++)
+        if (page_size == (1 << b)) page_shift = b;
+    AttnMixedTcArgs a{(const bf16*)q, q_stride, (const bf16*)kc, block_table, token_pos, cu_q, max_pages, page_size, page_shift, window, nh, nkv, d, hs, B,
                       scale, r1, r2, mix, gate, gate_stride, (bf16*)out};
     const size_t smem = at_plan(nh, nkv, d, hs).total;
     const dim3 grid((unsigned)(T / AT_BQ + B), (unsigned)(nh / hs));
