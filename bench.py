@@ -226,7 +226,7 @@ def llama_twin(z, vocab=32000, max_positions=4096):
 def run_design(args):
     """Prompt and decode throughput of a design at a few layer sizes, each beside the closest other
     model of the same width, feed-forward, head counts and number of layers (Vokelix beside LLaMA;
-    Vizosun beside Vokelix and LLaMA), through Engine.step; and
+    Vizosun beside Vokelix and LLaMA; Kudonex beside all three), through Engine.step; and
     where each of the two spends its time, kernel by kernel (the driver's activity records of one step).
     One JSON line per (size, model)."""
     import torch
