@@ -7,6 +7,8 @@
 // sequence) at `state_off` of the sequence's slot.  The taps are added oldest first whether a row comes from the
 // step or from the state, so the result does not depend on how a prompt was cut.  short_conv_state_kernel renews
 // the state from the step's rows afterwards (a launch of its own: the convolution reads the old one).
+#include <stdint.h>
+
 #include "common.cuh"
 
 struct ShortConvArgs {
@@ -21,24 +23,53 @@ struct ShortConvArgs {
     int ldo, o_off;
 };
 
-template <typename TO>
+__device__ __forceinline__ void sc_store(float* o, const float* v, int n) {
+    if (n == 4) *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+    else o[0] = v[0];
+}
+__device__ __forceinline__ void sc_store(bf16* o, const float* v, int n) {
+    if (n == 4) {
+        const unsigned lo = (unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(v[0])) | ((unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(v[1])) << 16);
+        const unsigned hi = (unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(v[2])) | ((unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(v[3])) << 16);
+        *reinterpret_cast<uint2*>(o) = make_uint2(lo, hi);
+    } else {
+        o[0] = __float2bfloat16_rn(v[0]);
+    }
+}
+
+// V channels per thread (4 where the widths, offsets and addresses are multiples of four, else 1); a channel's
+// arithmetic is the same in both.
+template <typename TO, int V>
 __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvArgs a) {
     pdl_grid_sync();
-    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     if (c >= a.C) return;
     const int b = a.token_seq[t], t0 = a.cu_q[b], i = t - t0, n_old = a.taps - 1;
     // one tap keeps no rows: such a call has no state and no slots
     const float* st = n_old > 0 ? a.state + (size_t)a.slots[b] * a.state_stride + a.state_off : nullptr;
-    float acc = 0.f;
+    float acc[V];
+#pragma unroll
+    for (int k = 0; k < V; k++) acc[k] = 0.f;
     for (int j = 0; j < a.taps; j++) {
         const int s = i - n_old + j;
-        const float v = s >= 0 ? a.x[(size_t)(t0 + s) * a.ldx + a.x_off + c] : st[(size_t)(n_old + s) * a.C + c];
-        acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);
+        const float* src = s >= 0 ? a.x + (size_t)(t0 + s) * a.ldx + a.x_off + c : st + (size_t)(n_old + s) * a.C + c;
+        float v[V];
+        if (V == 4) {
+            const float4 f = *reinterpret_cast<const float4*>(src);
+            v[0] = f.x, v[V > 1 ? 1 : 0] = f.y, v[V > 2 ? 2 : 0] = f.z, v[V > 3 ? 3 : 0] = f.w;
+        } else {
+            v[0] = src[0];
+        }
+#pragma unroll
+        for (int k = 0; k < V; k++) acc[k] = fmaf(a.w[(size_t)(c + k) * a.taps + j], v[k], acc[k]);
     }
-    if (a.bias) acc += a.bias[c];
-    if (a.act == 1) acc = acc / (1.0f + expf(-acc));
-    if (a.residual) acc += a.x[(size_t)t * a.ldx + a.x_off + c];
-    ((TO*)a.out)[(size_t)t * a.ldo + a.o_off + c] = from_f32<TO>(acc);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        if (a.bias) acc[k] += a.bias[c + k];
+        if (a.act == 1) acc[k] = acc[k] / (1.0f + expf(-acc[k]));
+        if (a.residual) acc[k] += a.x[(size_t)t * a.ldx + a.x_off + c + k];
+    }
+    sc_store((TO*)a.out + (size_t)t * a.ldo + a.o_off + c, acc, V);
 }
 
 // the last taps - 1 rows of (old state rows, then the step's rows), per sequence; a thread owns a channel and goes
@@ -65,9 +96,18 @@ extern "C" int illm_short_conv(const float* x, int T, int ldx, int x_off, int C,
     cudaStream_t s = (cudaStream_t)stream;
     const int by = (C + 255) / 256;
     if (by > 65535) return ILLM_ERR_BAD_ARG;
-    if (out_dtype == ILLM_BF16) illm_launch(short_conv_kernel<bf16>, dim3(T, by), dim3(256), 0, s, a);
-    else if (out_dtype == ILLM_F32) illm_launch(short_conv_kernel<float>, dim3(T, by), dim3(256), 0, s, a);
-    else return ILLM_ERR_BAD_ARG;
+    if (out_dtype != ILLM_BF16 && out_dtype != ILLM_F32) return ILLM_ERR_BAD_ARG;
+    const size_t osz = out_dtype == ILLM_BF16 ? 2 : 4;
+    const bool by4 = C % 4 == 0 && ldx % 4 == 0 && x_off % 4 == 0 && ldo % 4 == 0 && o_off % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+                     (uintptr_t)out % (4 * osz) == 0 && (taps == 1 || (state_stride % 4 == 0 && state_off % 4 == 0 && (uintptr_t)state % 16 == 0));
+    if (by4) {
+        const dim3 grid(T, (C / 4 + 127) / 128);
+        if (out_dtype == ILLM_BF16) illm_launch((short_conv_kernel<bf16, 4>), grid, dim3(128), 0, s, a);
+        else illm_launch((short_conv_kernel<float, 4>), grid, dim3(128), 0, s, a);
+    } else {
+        if (out_dtype == ILLM_BF16) illm_launch((short_conv_kernel<bf16, 1>), dim3(T, by), dim3(256), 0, s, a);
+        else illm_launch((short_conv_kernel<float, 1>), dim3(T, by), dim3(256), 0, s, a);
+    }
     if (update_state && taps > 1) illm_launch(short_conv_state_kernel, dim3(B, by), dim3(256), 0, s, a);
     return illm_launch_status();
 }
