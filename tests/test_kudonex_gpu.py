@@ -426,8 +426,9 @@ def test_running_maximum_starts_at_zero(tmp_path, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_choice_scores_below_zero(tmp_path, dtype):
-    """Corrections so far below zero that every choice score is negative: an expert outside the kept groups must
-    count as minus infinity, not as 0, or it would beat every allowed one.  The weights stay the plain scores."""
+    """Corrections so far below zero that every choice score is negative: an implementation that zeroed the experts
+    outside the kept groups instead of excluding them would let them beat every allowed one.  The weights stay the
+    plain scores."""
     cfg = pk.random_config((A,), taps=0, experts=8, top=2, group_count=4, group_keep=1)
 
     def edit(w):
