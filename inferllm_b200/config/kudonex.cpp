@@ -95,7 +95,7 @@ ModelSpec KudonexConfig::model_spec() const {
             mixer = PartSpec("mamba2", p);
         } else if (type == "attention") {
             // softmax attention over a sliding window without any rotation: the values are the keys, a logarithmic
-            // distance term is taken off the scores, the heads' scores are mixed before the softmax, and a full-width
+            // distance term is subtracted from the scores, the heads' scores are mixed before the softmax, and a full-width
             // sigmoid gate multiplies the concatenated heads
             const long long dim = take_int(m, "dim"), vdim = take_int(m, "vdim", dim);
             if (vdim != dim) throw ConfigError("config.json: " + where + "the values are the keys, so vdim must equal dim");

@@ -342,7 +342,7 @@ struct NoPosition : PositionEncoding {
 //
 // A second family of options changes the scores themselves and takes a kernel of its own (ops::attention_mixed):
 // `values` = "keys" (there is no value projection: the values are the keys as projected, and the cache entry keeps
-// keys only), `distance_bias` = "log1p" (r1_h ln(1 + r2_h (i - j)) is taken off the score of query i and key j; two
+// keys only), `distance_bias` = "log1p" (r1_h ln(1 + r2_h (i - j)) is subtracted from the score of query i and key j; two
 // numbers per head, tensors "r1" and "r2"), `head_mix` = true (before the softmax the heads' scores are mixed,
 // score_h <- sum_g M[h, g] score_g, tensor "mix" [heads, heads]) and `out_gate` = "sigmoid" (a full-width gate
 // projection of the mixer's input; the concatenated heads are multiplied by its sigmoid element by element).  The

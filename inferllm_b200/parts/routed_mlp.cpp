@@ -12,8 +12,8 @@
 //
 // A second way to choose, `scoring` = "softmax_all": the scores are s = softmax(z) over ALL experts; the `top` experts
 // with the largest s + correction are chosen (the correction, tensor "correction" [experts], present if
-// `choice_correction`, never enters the weights); with `groups` {count, keep} the experts form `count` equal groups of
-// neighbours, a group's score is its largest corrected score, and only experts of the `keep` best groups can be
+// `choice_correction`, never enters the weights); with `groups` {count, keep} the experts form `count` equal runs of
+// adjacent experts (groups), a group's score is its largest corrected score, and only experts of the `keep` best groups can be
 // chosen; the weights are the chosen experts' s, as they are unless `renormalize`.  `shared` {intermediate_size,
 // activation, names} adds a gated feed-forward that every token goes through (a "gated_mlp" part below the prefix
 // `shared_prefix`), its float32 output summed with the experts' in the kernel that combines them.

@@ -3,7 +3,7 @@ recurrence and every attention row a literal loop.  It shares nothing with the l
 engine with it.
 
 A model is (cfg, W): cfg the config.json object, W a dict name -> float64 array.  Everything runs on one
-sequence: x is [n, width], positions count from 0.
+sequence: x is [n, width], the first token has position 0.
 """
 import math
 
