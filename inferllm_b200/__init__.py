@@ -10,13 +10,13 @@ this package is its Python face.
 """
 from .binding import (CacheError, CacheFull, ConfigError, EngineError, KernelError, KernelLibraryError, RequestTooLong,
                       WeightError, library_errors)
-from .config import (ArchConfig, LlamaConfig, VokelixConfig, VizosunConfig, KudonexConfig, config_from_dict, config_from_folder, register_architecture,
+from .config import (ArchConfig, LlamaConfig, VokelixConfig, VizosunConfig, KudonexConfig, TukulornConfig, config_from_dict, config_from_folder, register_architecture,
                      registered_architectures, unregister_architecture)
 from .engine import Engine, EngineOptions, GenerationResult, Limits, Model, ModelConfig, StepItem, generate
 from .sampling import Sampler, SamplingParams
 from .weights import write_random_model
 
-__all__ = ["ArchConfig", "CacheError", "CacheFull", "ConfigError", "LlamaConfig", "VokelixConfig", "VizosunConfig", "KudonexConfig", "Engine", "EngineError", "EngineOptions",
+__all__ = ["ArchConfig", "CacheError", "CacheFull", "ConfigError", "LlamaConfig", "VokelixConfig", "VizosunConfig", "KudonexConfig", "TukulornConfig", "Engine", "EngineError", "EngineOptions",
            "GenerationResult", "KernelError", "KernelLibraryError", "Limits", "Model", "ModelConfig", "RequestTooLong", "StepItem",
            "generate", "config_from_dict", "config_from_folder", "register_architecture", "registered_architectures",
            "unregister_architecture", "Sampler", "SamplingParams", "WeightError", "write_random_model", "library_errors"]

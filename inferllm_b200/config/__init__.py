@@ -224,7 +224,17 @@ class KudonexConfig(LibraryConfig):
     architecture = "Kudonex"
 
 
-_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig, "Vokelix": VokelixConfig, "Vizosun": VizosunConfig, "Kudonex": KudonexConfig}
+class TukulornConfig(LibraryConfig):
+    """The Tukulorn decoder (`config/tukulorn.h`): `layers` (a list of {type: "attention" | "latent_attention",
+    mixer: {...}, mlp: {kind: "dense", ff} | {kind: "moe", expert: {ff, limit}, router: {experts, top, scale, groups:
+    {count, keep}}} | None}), `width`, `vocab`, `norm` ({eps}), optionally `loop` ({start, stop, times}) and
+    `max_positions`.  The dictionary names the class under `architecture`."""
+
+    architecture = "Tukulorn"
+
+
+_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig, "Vokelix": VokelixConfig, "Vizosun": VizosunConfig, "Kudonex": KudonexConfig,
+                                "Tukulorn": TukulornConfig}
 _CALLBACKS = {}      # name -> (ctypes callback, holder of the last returned text): kept alive while registered
 
 
@@ -267,7 +277,7 @@ def register_architecture(name: str, config_cls: type, aliases=()):
 def unregister_architecture(name: str):
     _b.check(_b.lib().illm_unregister_architecture(name.encode()))
     _CALLBACKS.pop(name, None)
-    if _PY_CLASSES.get(name) not in (LlamaConfig, VokelixConfig, VizosunConfig, KudonexConfig):
+    if _PY_CLASSES.get(name) not in (LlamaConfig, VokelixConfig, VizosunConfig, KudonexConfig, TukulornConfig):
         _PY_CLASSES.pop(name, None)
 
 

@@ -213,6 +213,7 @@ void register_llama_architecture();     // config/llama.cpp
 void register_vokelix_architecture();   // config/vokelix.cpp
 void register_vizosun_architecture();   // config/vizosun.cpp
 void register_kudonex_architecture();   // config/kudonex.cpp
+void register_tukulorn_architecture();  // config/tukulorn.cpp
 
 static void ensure_builtin() {
     static bool done = false;
@@ -222,6 +223,7 @@ static void ensure_builtin() {
         register_vokelix_architecture();
         register_vizosun_architecture();
         register_kudonex_architecture();
+        register_tukulorn_architecture();
     }
 }
 

@@ -64,7 +64,8 @@ struct LayerSpec {
 // only reads what an earlier entry of the same step wrote (a layer attending to another layer's
 // keys and values).
 // `reenter`: before the layer runs, the stream is replaced by the model's re-entry map of [stream; embedding
-// output] (ModelSpec::reentry), as a model does that runs some of its layers several times in a row.
+// output] (ModelSpec::reentry), or, with the re-entry kind "add_embedding", the embedding output is added to it, as a
+// model does that runs some of its layers several times in a row.
 struct ScheduleEntry {
     int layer = 0, cache = 0;
     bool writes = true;
@@ -79,7 +80,8 @@ struct ModelSpec {
     PartSpec final_norm;   // params: name, size, eps, ...
     PartSpec head;         // params: name, tied, vocab_size, hidden_size, ...
     // A feed-forward part [2 hidden -> hidden] (kind "" = none) applied to the stream joined with the embedding
-    // output before every schedule entry marked `reenter`; params: name (tensor-name prefix), ...
+    // output before every schedule entry marked `reenter`; params: name (tensor-name prefix), ...  The kind
+    // "add_embedding" has no tensors: the embedding output is added to the stream.
     PartSpec reentry;
     bool has_bos = false;
     long long bos_token_id = 0;

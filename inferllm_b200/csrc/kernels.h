@@ -141,6 +141,21 @@ int illm_gather_i32(const int* src, const int* idx, int* dst, int n, void* strea
 int illm_window_gather(const int* window, int n_last, const int* rows, int* dst, int n, void* stream);
 int illm_window_put(int* window, int n_last, const int* rows, int col, const int* toks, int n, void* stream);
 
+// entry points with further parameters (the shorter forms above call them)
+int illm_qk_prep_ex(const void* x, int x_dtype, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int d, int dv, const float* bq, const float* bk, const float* bv, const float* wq, const float* wk, float eps, const float* cos_sin, int rot, int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* q_out, void* kc, void* vc, int act_dtype, int T, int* err, float qt_coef, int qt_every, void* stream);
+int illm_head_gemm_ex(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, int T, int heads, int N, int K, int nn, int x_ld, int x_hs, int y_ld, int y_hs, void* stream);
+int illm_moe_route_ex2(const float* logits, const float* bias, int T, int E, int top, int bm, int scoring, int groups, int keep, int renorm, int group_top, float sum_eps, float weight_scale, int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
+int illm_moe_gemm_ex(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated, int act, float act_limit, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows, void* stream);
+int illm_moe_gemm_tc_ex(const void* xs, const void* w, void* y, int P, int E, int N, int K, int gated, int act, float act_limit, int tiles, const int* tile_expert, const int* tile_row0, const int* tile_rows, int* err, void* stream);
+// attention_diff.cu
+int illm_attention_diff(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int dv, int page_size, int window, float scale, float lambda, float eps, float out_scale, void* stream);
+// latent_attention.cu
+int illm_latent_attention_any_gated(const void* q, const void* kc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int H, int R, int page_size, int window, float scale, const float* gate, int gate_stride, void* stream);
+int illm_latent_rope_prep(const float* x, int ld, int q_off, int H, int d, int dr, int c_off, int R, const float* wkv, float eps, const float* cos_sin, int rot, int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* q_nope, int q_f32, void* qa, void* kc, int act_dtype, int T, int* err, void* stream);
+// stream_ops.cu
+int illm_add_bias(void* y, int dtype, const float* b, int T, int H, void* stream);
+int illm_scaled_add_rmsnorm(float* resid, const float* delta, const float* bias, const float* ls, const float* w, void* y, int act_dtype, int T, int H, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,32 +51,54 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
     for (int k = lane + 32; k < top; k += 32) weight[(size_t)t * top + k] /= sum;
 }
 
-// Routing by scores over ALL experts: s = softmax(z); the choice looks at s + choice_bias (the bias never enters the
-// weights), optionally confined to the `keep` best of `groups` equal groups of neighbouring experts (a group's score
-// is its largest choice score; experts of other groups cannot be chosen, whatever their score); the weights are the
-// chosen experts' s, divided by their sum only if `renorm`.  Among equal scores the lowest index wins.  A warp per
-// token; up to 32 groups.
+// Routing by scores over ALL experts: s = softmax(z), or with `sigmoid` s_e = 1 / (1 + exp(-z_e)); the choice looks at
+// s + choice_bias (the bias never enters the weights), optionally confined to the `keep` best of `groups` equal groups
+// of neighbouring experts (a group's score is the sum of its `group_top` largest choice scores, 1: the largest;
+// experts of other groups cannot be chosen, whatever their score); the weights are the chosen experts' s, divided by
+// their sum (+ sum_eps) only if `renorm`, then times weight_scale.  Among equal scores the lowest index wins.  A warp
+// per token; up to 32 groups, group_top up to 4.
 __global__ void moe_route_scored_kernel(const float* __restrict__ logits, const float* __restrict__ choice_bias, int T, int E, int top, int groups,
-                                        int keep, int renorm, int* __restrict__ expert, float* __restrict__ weight) {
+                                        int keep, int renorm, int sigmoid, int group_top, float sum_eps, float weight_scale,
+                                        int* __restrict__ expert, float* __restrict__ weight) {
     pdl_grid_sync();
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     const float* z = logits + (size_t)t * E;
-    float zmax = -INFINITY;
-    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
-    zmax = warp_max(zmax);
-    float den = 0.f;
-    for (int e = lane; e < E; e += 32) den += expf(z[e] - zmax);
-    den = warp_sum(den);
+    float zmax = 0.f, den = 1.f;
+    if (!sigmoid) {
+        zmax = -INFINITY;
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+        zmax = warp_max(zmax);
+        den = 0.f;
+        for (int e = lane; e < E; e += 32) den += expf(z[e] - zmax);
+        den = warp_sum(den);
+    }
+    auto score = [&](int e) { return sigmoid ? 1.0f / (1.0f + expf(-z[e])) : expf(z[e] - zmax) / den; };
     const int per = E / groups;
     unsigned kept = 0xffffffffu;       // bit g: group g may be chosen from
     if (groups > 1 && keep < groups) {
         float mine = -INFINITY;        // lane g holds group g's score
         for (int g = 0; g < groups; g++) {
-            float best = -INFINITY;
-            for (int e = g * per + lane; e < (g + 1) * per; e += 32) best = fmaxf(best, expf(z[e] - zmax) / den + (choice_bias ? choice_bias[e] : 0.f));
-            best = warp_max(best);
-            if (lane == g) mine = best;
+            float gs = 0.f;
+            int took[4] = {-1, -1, -1, -1};
+            for (int r = 0; r < group_top && r < per; r++) {       // the group's r-th largest choice score
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                for (int e = g * per + lane; e < (g + 1) * per; e += 32) {
+                    if (e == took[0] || e == took[1] || e == took[2] || e == took[3]) continue;
+                    const float v = score(e) + (choice_bias ? choice_bias[e] : 0.f);
+                    if (v > bv || bi == 0x7fffffff) { bv = v; bi = e; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+                }
+                took[r] = bi;
+                gs = r == 0 ? bv : gs + bv;
+            }
+            if (lane == g) mine = gs;
         }
         kept = 0;
         for (int k = 0; k < keep; k++) {
@@ -100,7 +122,7 @@ __global__ void moe_route_scored_kernel(const float* __restrict__ logits, const 
             bool taken = false;
             for (int j = 0; j < k; j++) taken |= expert[(size_t)t * top + j] == e;
             if (taken) continue;
-            const float sc = expf(z[e] - zmax) / den;
+            const float sc = score(e);
             const float v = sc + (choice_bias ? choice_bias[e] : 0.f);
             if (v > bv || bi == 0x7fffffff) { bv = v; bi = e; bs = sc; }
         }
@@ -117,8 +139,12 @@ __global__ void moe_route_scored_kernel(const float* __restrict__ logits, const 
         }
         __syncwarp();
     }
-    if (renorm)
-        for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] /= sum;
+    if (renorm || weight_scale != 1.f)
+        for (int k = lane; k < top; k += 32) {
+            float w = weight[(size_t)t * top + k];
+            if (renorm) w /= sum + sum_eps;
+            weight[(size_t)t * top + k] = w * weight_scale;
+        }
 }
 
 // dynamic shared memory: 3 E + 1 ints
@@ -156,11 +182,16 @@ moe_layout_kernel(const int* __restrict__ expert, int P, int E, int bm, int* __r
     }
 }
 
-__device__ __forceinline__ float moe_act(float v, int act) {
-    if (act == 1) return v / (1.0f + expf(-v));
-    if (act == 2) return fmaxf(v, 0.f);
-    if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-    return v;
+// act(gate) * up; act 4 is the clamped form g = min(gate, limit), u = clamp(up, -limit, limit): g sigmoid(1.702 g) (u + 1)
+__device__ __forceinline__ float moe_gated(float v, float u, int act, float limit) {
+    if (act == 1) return v / (1.0f + expf(-v)) * u;
+    if (act == 2) return fmaxf(v, 0.f) * u;
+    if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))) * u;
+    if (act == 4) {
+        const float g = fminf(v, limit), c = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (c + 1.0f);
+    }
+    return v * u;
 }
 
 #define MOE_BN 64
@@ -171,7 +202,7 @@ __device__ __forceinline__ float moe_act(float v, int act) {
 // y [P, Nw / 2] = act(gate) * up; else x [P, K] by row and y [P, Nw].
 template <typename TX, typename TW, typename TY, int BM, bool GATED>
 __global__ void __launch_bounds__(256)
-moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int Nw, int K, int top, int act,
+moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int Nw, int K, int top, int act, float act_limit,
                 const int* __restrict__ pair_of_row, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                 const int* __restrict__ tile_rows) {
     pdl_grid_sync();
@@ -225,7 +256,7 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restri
 #pragma unroll
             for (int j = 0; j < 4; j += 2) {
                 const int n = n0 + tx * 4 + j;
-                if (n + 1 < Nw) y[(size_t)(row0 + m) * (Nw / 2) + n / 2] = from_f32<TY>(moe_act(acc[i][j], act) * acc[i][j + 1]);
+                if (n + 1 < Nw) y[(size_t)(row0 + m) * (Nw / 2) + n / 2] = from_f32<TY>(moe_gated(acc[i][j], acc[i][j + 1], act, act_limit));
             }
         } else {
 #pragma unroll
@@ -264,7 +295,7 @@ __device__ __forceinline__ void mm_mma(float* c, const unsigned* a, unsigned b0,
 
 template <typename TY, bool GATED>
 __global__ void __launch_bounds__(256)
-moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* __restrict__ y, int N, int K, int top, int act,
+moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* __restrict__ y, int N, int K, int top, int act, float act_limit,
                     const int* __restrict__ pair_of_row, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                     const int* __restrict__ tile_rows) {
     pdl_grid_sync();
@@ -357,7 +388,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* 
                 const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + (c & 1);
                 if (m >= rows) continue;
                 if (GATED) {          // columns n, n + 1 are gate and up of output n / 2
-                    if (n + 1 < N) y[(size_t)(row0 + m) * (N / 2) + n / 2] = from_f32<TY>(moe_act(acc[0][i][j][c], act) * acc[0][i][j][c + 1]);
+                    if (n + 1 < N) y[(size_t)(row0 + m) * (N / 2) + n / 2] = from_f32<TY>(moe_gated(acc[0][i][j][c], acc[0][i][j][c + 1], act, act_limit));
                 } else if (n < N) {
                     y[(size_t)(row0 + m) * N + n] = from_f32<TY>(acc[0][i][j][c]);
                 }
@@ -406,18 +437,30 @@ extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int
     return illm_moe_route_ex(logits, bias, T, E, top, bm, 0, 1, 1, 1, expert, weight, row_of_pair, pair_of_row, tile_expert, tile_row0, tile_rows, stream);
 }
 
-// scoring 0: the `top` largest logits + bias, weights the softmax over the chosen; scoring 1: scores are the softmax
-// over all experts, bias enters the choice only, `keep` of `groups` groups may be chosen from, weights divided by
-// their sum if renorm (moe_route_scored_kernel)
+extern "C" int illm_moe_route_ex2(const float* logits, const float* bias, int T, int E, int top, int bm, int scoring, int groups, int keep, int renorm,
+                                  int group_top, float sum_eps, float weight_scale, int* expert, float* weight, int* row_of_pair, int* pair_of_row,
+                                  int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
 extern "C" int illm_moe_route_ex(const float* logits, const float* bias, int T, int E, int top, int bm, int scoring, int groups, int keep, int renorm,
                                  int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows,
                                  void* stream) {
+    return illm_moe_route_ex2(logits, bias, T, E, top, bm, scoring, groups, keep, renorm, 1, 0.f, 1.f, expert, weight, row_of_pair, pair_of_row, tile_expert,
+                              tile_row0, tile_rows, stream);
+}
+// scoring 0: the `top` largest logits + bias, weights the softmax over the chosen; scoring 1: scores are the softmax
+// over all experts, 2: the sigmoid of every logit; with 1 and 2 the bias enters the choice only, `keep` of `groups` groups
+// (scored by the sum of their group_top largest) may be chosen from, weights divided by their sum + sum_eps if renorm and
+// multiplied by weight_scale (moe_route_scored_kernel)
+extern "C" int illm_moe_route_ex2(const float* logits, const float* bias, int T, int E, int top, int bm, int scoring, int groups, int keep, int renorm,
+                                  int group_top, float sum_eps, float weight_scale, int* expert, float* weight, int* row_of_pair, int* pair_of_row,
+                                  int* tile_expert, int* tile_row0, int* tile_rows, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || (bm != 16 && bm != 64 && bm != 128) || (size_t)(3 * E + 1) * sizeof(int) > 160 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    if (scoring == 1) {
-        if (groups < 1 || groups > 32 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top) return ILLM_ERR_BAD_ARG;
-        illm_launch(moe_route_scored_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, groups, keep, renorm, expert, weight);
+    if (scoring == 1 || scoring == 2) {
+        if (groups < 1 || groups > 32 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top || group_top < 1 || group_top > 4)
+            return ILLM_ERR_BAD_ARG;
+        illm_launch(moe_route_scored_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, groups, keep, renorm, scoring == 2 ? 1 : 0,
+                    group_top, sum_eps, weight_scale, expert, weight);
     } else if (scoring == 0) {
         illm_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, expert, weight);
     } else {
@@ -437,9 +480,19 @@ extern "C" int illm_moe_route_ex(const float* logits, const float* bias, int T, 
 // w [E, N, K].  gated != 0: x [T, K] (x_dtype), the matrix's rows 2i, 2i + 1 gate and up of output i, y [T * top, N / 2] in
 // the dtype of x; else x [T * top, K], y [T * top, N] float32.
 // tensor_cores != 0 (bfloat16, K % 8 == 0, tiles of 64 rows): the mma kernel.
+extern "C" int illm_moe_gemm_ex(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated,
+                                int act, float act_limit, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert,
+                                const int* tile_row0, const int* tile_rows, void* stream);
 extern "C" int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated,
                              int act, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0,
                              const int* tile_rows, void* stream) {
+    return illm_moe_gemm_ex(x, x_dtype, w, w_dtype, y, T, top, E, N, K, gated, act, 0.f, bm, tensor_cores, pair_of_row, tile_expert, tile_row0, tile_rows,
+                            stream);
+}
+// act_limit: the limit of the clamped activation (act 4)
+extern "C" int illm_moe_gemm_ex(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated,
+                                int act, float act_limit, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert,
+                                const int* tile_row0, const int* tile_rows, void* stream) {
     if (T <= 0) return 0;
     if (N <= 0 || K <= 0 || x_dtype != w_dtype || (bm != 16 && bm != 64) || (gated && (N & 1))) return ILLM_ERR_BAD_ARG;
     const int tiles = illm_moe_max_tiles(T, top, E, bm);
@@ -456,16 +509,16 @@ extern "C" int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dt
             raised = true;
         }
         if (gated)
-            illm_launch(moe_gemm_mma_kernel<bf16, true>, mgrid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (bf16*)y, N, K, top, act,
+            illm_launch(moe_gemm_mma_kernel<bf16, true>, mgrid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (bf16*)y, N, K, top, act, act_limit,
                         pair_of_row, tile_expert, tile_row0, tile_rows);
         else
-            illm_launch(moe_gemm_mma_kernel<float, false>, mgrid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (float*)y, N, K, top, act,
+            illm_launch(moe_gemm_mma_kernel<float, false>, mgrid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (float*)y, N, K, top, act, act_limit,
                         pair_of_row, tile_expert, tile_row0, tile_rows);
         return illm_launch_status();
     }
     dim3 grid((N + MOE_BN - 1) / MOE_BN, tiles);
 #define ILLM_MOE(TX, TY, BM, G)                                                                                                       \
-    illm_launch(moe_gemm_kernel<TX, TX, TY, BM, G>, grid, dim3(256), 0, s, (const TX*)x, (const TX*)w, (TY*)y, N, K, top, act, pair_of_row, \
+    illm_launch(moe_gemm_kernel<TX, TX, TY, BM, G>, grid, dim3(256), 0, s, (const TX*)x, (const TX*)w, (TY*)y, N, K, top, act, act_limit, pair_of_row, \
                 tile_expert, tile_row0, tile_rows)
     if (x_dtype == ILLM_BF16) {
         if (gated) { if (bm == 16) ILLM_MOE(bf16, bf16, 16, true); else ILLM_MOE(bf16, bf16, 64, true); }

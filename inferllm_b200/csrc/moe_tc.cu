@@ -13,17 +13,22 @@
 
 #define MT_MAX_STAGES 8
 
-__device__ __forceinline__ float mt_act(float v, int act) {
-    if (act == 1) return v / (1.0f + __expf(-v));
-    if (act == 2) return fmaxf(v, 0.f);
-    if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-    return v;
+// act(gate) * up; act 4: g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(1.702 g) (u + 1)
+__device__ __forceinline__ float mt_gated(float v, float u, int act, float limit) {
+    if (act == 1) return v / (1.0f + __expf(-v)) * u;
+    if (act == 2) return fmaxf(v, 0.f) * u;
+    if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))) * u;
+    if (act == 4) {
+        const float g = fminf(v, limit), c = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + __expf(-1.702f * g)) * (c + 1.0f);
+    }
+    return v * u;
 }
 
 template <int BN, typename TOut, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TOut* __restrict__ C, int ldc,
-                   int n_per_expert, int n_k, int STAGES, int act, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                   int n_per_expert, int n_k, int STAGES, int act, float act_limit, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                    const int* __restrict__ tile_rows, int* __restrict__ err) {
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
@@ -111,7 +116,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     TOut* dst = C + ra * ldc + (nb0 + c0) / 2;
                     float o[8];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) o[j] = mt_act(v[2 * j], act) * v[2 * j + 1];
+                    for (int j = 0; j < 8; j++) o[j] = mt_gated(v[2 * j], v[2 * j + 1], act, act_limit);
                     if (nb0 + c0 + 16 <= n_per_expert && (ldc & 7) == 0) {
                         store8(dst, o);
                     } else {
@@ -164,7 +169,7 @@ static int mt_make_map(CUtensorMap* map, const void* ptr, long long rows, long l
 }
 
 template <int BN, typename TOut, bool GATED>
-static int mt_launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* y, int ldc, int N, int k_iters, int tiles, int act, const int* tile_expert,
+static int mt_launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* y, int ldc, int N, int k_iters, int tiles, int act, float act_limit, const int* tile_expert,
                      const int* tile_row0, const int* tile_rows, int* err, cudaStream_t s) {
     const int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     // a ring that leaves room for TWO blocks on an SM (two stages of 48 KB, three of 32 KB): one block's epilogue then runs
@@ -178,15 +183,22 @@ static int mt_launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* y, int 
     auto kern = moe_gemm_tc_kernel<BN, TOut, GATED>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    illm_launch(kern, dim3(tiles, (N + BN - 1) / BN), dim3(TC_THREADS), smem, s, ma, mb, y, ldc, N, k_iters, stages, act, tile_expert, tile_row0,
+    illm_launch(kern, dim3(tiles, (N + BN - 1) / BN), dim3(TC_THREADS), smem, s, ma, mb, y, ldc, N, k_iters, stages, act, act_limit, tile_expert, tile_row0,
                 tile_rows, err);
     return illm_launch_status();
 }
 
 // xs [P, K] bfloat16: the rows in the experts' order; w [E * N, K] bfloat16; the tile list with tiles of up to 128 rows
 // (`tiles` entries).  gated != 0: y [P, N / 2] bfloat16 = act(gate) * up of the matrix's row pairs; else y [P, N] float32.
+extern "C" int illm_moe_gemm_tc_ex(const void* xs, const void* w, void* y, int P, int E, int N, int K, int gated, int act, float act_limit, int tiles,
+                                   const int* tile_expert, const int* tile_row0, const int* tile_rows, int* err, void* stream);
 extern "C" int illm_moe_gemm_tc(const void* xs, const void* w, void* y, int P, int E, int N, int K, int gated, int act, int tiles,
                                 const int* tile_expert, const int* tile_row0, const int* tile_rows, int* err, void* stream) {
+    return illm_moe_gemm_tc_ex(xs, w, y, P, E, N, K, gated, act, 0.f, tiles, tile_expert, tile_row0, tile_rows, err, stream);
+}
+// act_limit: the limit of the clamped activation (act 4)
+extern "C" int illm_moe_gemm_tc_ex(const void* xs, const void* w, void* y, int P, int E, int N, int K, int gated, int act, float act_limit, int tiles,
+                                   const int* tile_expert, const int* tile_row0, const int* tile_rows, int* err, void* stream) {
     if (P <= 0) return 0;
     if (N <= 0 || K <= 0 || (K & 7) || (gated && (N & 1)) || ((uintptr_t)xs & 15) || ((uintptr_t)w & 15) || tiles <= 0) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
@@ -197,9 +209,9 @@ extern "C" int illm_moe_gemm_tc(const void* xs, const void* w, void* y, int P, i
     if ((rc = mt_make_map(&ma, xs, P, K, TC_BM)) != 0) return rc;
     if ((rc = mt_make_map(&mb, w, (long long)E * N, K, bn)) != 0) return rc;
     if (gated) {
-        if (bn == 256) return mt_launch<256, bf16, true>(ma, mb, (bf16*)y, N / 2, N, k_iters, tiles, act, tile_expert, tile_row0, tile_rows, err, s);
-        return mt_launch<128, bf16, true>(ma, mb, (bf16*)y, N / 2, N, k_iters, tiles, act, tile_expert, tile_row0, tile_rows, err, s);
+        if (bn == 256) return mt_launch<256, bf16, true>(ma, mb, (bf16*)y, N / 2, N, k_iters, tiles, act, act_limit, tile_expert, tile_row0, tile_rows, err, s);
+        return mt_launch<128, bf16, true>(ma, mb, (bf16*)y, N / 2, N, k_iters, tiles, act, act_limit, tile_expert, tile_row0, tile_rows, err, s);
     }
-    if (bn == 256) return mt_launch<256, float, false>(ma, mb, (float*)y, N, N, k_iters, tiles, act, tile_expert, tile_row0, tile_rows, err, s);
-    return mt_launch<128, float, false>(ma, mb, (float*)y, N, N, k_iters, tiles, act, tile_expert, tile_row0, tile_rows, err, s);
+    if (bn == 256) return mt_launch<256, float, false>(ma, mb, (float*)y, N, N, k_iters, tiles, act, act_limit, tile_expert, tile_row0, tile_rows, err, s);
+    return mt_launch<128, float, false>(ma, mb, (float*)y, N, N, k_iters, tiles, act, act_limit, tile_expert, tile_row0, tile_rows, err, s);
 }

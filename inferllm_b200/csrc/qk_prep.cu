@@ -27,6 +27,8 @@ struct QkPrepArgs {
     int max_pages, page_size;
     void *q_out, *kc, *vc;
     int* err;
+    float qt_coef;      // query temperature: q *= 1 + qt_coef * ln((p + 1) / qt_every + 1), the division whole-numbered
+    int qt_every;       // 0: none
 };
 
 __device__ __forceinline__ float rotated(const float* buf, int e, int rot, int pairs, const float* cs) {
@@ -62,9 +64,11 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(QkPrepArgs a) {
         p = 0;
     }
     float ssq = 0.f, ssk = 0.f;
+    const float q_temp = a.qt_every > 0 ? 1.0f + a.qt_coef * logf((float)((a.token_pos[t] + 1) / a.qt_every + 1)) : 1.0f;
     for (int c = threadIdx.x; c < nq; c += blockDim.x) {
         float v = to_f32(x[a.q_off + c]);
         if (a.bq) v += a.bq[c];
+        if (a.qt_every > 0) v *= q_temp;
         buf[c] = v;
         ssq += v * v;
     }
@@ -114,15 +118,30 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(QkPrepArgs a) {
     }
 }
 
+// the same with a temperature on the queries that grows with the position (qt_every 0: none), applied behind the bias
+extern "C" int illm_qk_prep_ex(const void* x, int x_dtype, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int d, int dv, const float* bq,
+                               const float* bk, const float* bv, const float* wq, const float* wk, float eps, const float* cos_sin, int rot,
+                               int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages,
+                               int page_size, void* q_out, void* kc, void* vc, int act_dtype, int T, int* err, float qt_coef, int qt_every,
+                               void* stream);
 extern "C" int illm_qk_prep(const void* x, int x_dtype, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int d, int dv, const float* bq,
                             const float* bk, const float* bv, const float* wq, const float* wk, float eps, const float* cos_sin, int rot,
                             int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages,
                             int page_size, void* q_out, void* kc, void* vc, int act_dtype, int T, int* err, void* stream) {
+    return illm_qk_prep_ex(x, x_dtype, ld, q_off, k_off, v_off, nh, nkv, d, dv, bq, bk, bv, wq, wk, eps, cos_sin, rot, pairs, n_pos, token_pos, token_seq,
+                           block_table, max_pages, page_size, q_out, kc, vc, act_dtype, T, err, 0.f, 0, stream);
+}
+extern "C" int illm_qk_prep_ex(const void* x, int x_dtype, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int d, int dv, const float* bq,
+                               const float* bk, const float* bv, const float* wq, const float* wk, float eps, const float* cos_sin, int rot,
+                               int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages,
+                               int page_size, void* q_out, void* kc, void* vc, int act_dtype, int T, int* err, float qt_coef, int qt_every,
+                               void* stream) {
     if (T <= 0) return 0;
+    if (qt_every < 0) return ILLM_ERR_BAD_ARG;
     if (nh <= 0 || d <= 0 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !q_out) return ILLM_ERR_BAD_ARG;
     if (k_off >= 0 && (nkv <= 0 || dv <= 0)) return ILLM_ERR_BAD_ARG;      // v_off < 0 with k_off >= 0: keys alone are stored
     QkPrepArgs a{x, ld, q_off, k_off, v_off, nh, nkv, d, dv, bq, bk, bv, wq, wk, eps, cos_sin, rot, pairs, n_pos,
-                 token_pos, token_seq, block_table, max_pages, page_size, q_out, kc, vc, err};
+                 token_pos, token_seq, block_table, max_pages, page_size, q_out, kc, vc, err, qt_coef, qt_every};
     const size_t smem = (size_t)(nh * d + (k_off >= 0 ? nkv * d : 0)) * sizeof(float);
     if (smem > 200 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;

@@ -145,3 +145,68 @@ extern "C" int illm_add2_rmsnorm(float* resid, const float* d1, const float* d2,
     else return ILLM_ERR_BAD_ARG;
     return illm_launch_status();
 }
+
+// scaled_add_rmsnorm: resid[t, :] += (delta[t, :] (+ bias)) * ls   (a sublayer's output through a per-channel layer scale,
+// all float32), and, if w is given, y[t, :] = resid[t, :] / sqrt(mean(resid^2) + eps) * w in the activation dtype: the
+// layer scale folded into the next norm.  A block per row, the row kept in shared memory between the two passes.
+template <typename TY>
+__global__ void __launch_bounds__(1024)
+scaled_add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta, const float* __restrict__ bias, const float* __restrict__ ls,
+                          const float* __restrict__ w, TY* __restrict__ y, int H, float eps) {
+    pdl_grid_sync();
+    extern __shared__ __align__(16) float row_sm[];
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float dl = delta[base + c];
+        if (bias) dl += bias[c];
+        const float v = fmaf(dl, ls[c], resid[base + c]);
+        resid[base + c] = v;
+        row_sm[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!w) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) y[base + c] = from_f32<TY>((row_sm[c] * inv) * w[c]);
+}
+
+extern "C" int illm_scaled_add_rmsnorm(float* resid, const float* delta, const float* bias, const float* ls, const float* w, void* y, int act_dtype,
+                                       int T, int H, float eps, void* stream) {
+    if (T <= 0 || H <= 0) return 0;
+    if (!delta || !ls || (w && !y) || (size_t)H * sizeof(float) > 200 * 1024) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)H * sizeof(float);
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        raised = true;
+    }
+    int threads = (H / 4 + 31) / 32 * 32;       // the block size depends on the width alone
+    threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
+    if (act_dtype == ILLM_BF16) illm_launch(scaled_add_rmsnorm_kernel<bf16>, dim3(T), dim3(threads), smem, s, resid, delta, bias, ls, w, (bf16*)y, H, eps);
+    else if (act_dtype == ILLM_F32) illm_launch(scaled_add_rmsnorm_kernel<float>, dim3(T), dim3(threads), smem, s, resid, delta, bias, ls, w, (float*)y, H, eps);
+    else return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
+}
+
+// add_bias: y[t, c] += b[c] (b float32), in place, for a projection with a bias whose product kernel has no bias epilogue
+template <typename TA>
+__global__ void add_bias_kernel(TA* __restrict__ y, const float* __restrict__ b, int H, long long n) {
+    pdl_grid_sync();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = from_f32<TA>(to_f32(y[i]) + b[i % H]);
+}
+extern "C" int illm_add_bias(void* y, int dtype, const float* b, int T, int H, void* stream) {
+    if (T <= 0 || H <= 0) return 0;
+    if (!y || !b) return ILLM_ERR_BAD_ARG;
+    const long long n = (long long)T * H;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ILLM_BF16) illm_launch(add_bias_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)y, b, H, n);
+    else if (dtype == ILLM_F32) illm_launch(add_bias_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)y, b, H, n);
+    else return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
+}

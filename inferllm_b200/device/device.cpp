@@ -205,12 +205,17 @@ void Device::library_gemm_bf16(const void* x, const void* w, void* out, DType ou
                           std::to_string(M) + ", " + std::to_string(K) + "] x [" + std::to_string(N) + ", " + std::to_string(K) + "]^T");
 }
 
-void Device::library_gemm_bf16_heads(const void* x, const void* w, void* out, int M, int N, int K, int batch, bool transposed) {
+void Device::library_gemm_bf16_heads(const void* x, const void* w, void* out, int M, int N, int K, int batch, bool transposed, int x_ld,
+                                     long long x_head_stride, int out_ld, long long out_head_stride) {
     const float alpha = 1.f, beta = 0.f;
-    // per head, in column-major terms: out_b [N, M] (ld batch * N) = op(w_b) [N, K] . x_b [K, M] (ld batch * K)
+    if (!x_ld) x_ld = batch * K;
+    if (!x_head_stride) x_head_stride = K;
+    if (!out_ld) out_ld = batch * N;
+    if (!out_head_stride) out_head_stride = N;
+    // per head, in column-major terms: out_b [N, M] (ld out_ld) = op(w_b) [N, K] . x_b [K, M] (ld x_ld)
     cublasStatus_t st = cublasGemmStridedBatchedEx(
         (cublasHandle_t)cublas_, transposed ? CUBLAS_OP_N : CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, transposed ? N : K,
-        (long long)N * K, x, CUDA_R_16BF, batch * K, (long long)K, &beta, out, CUDA_R_16BF, batch * N, (long long)N, batch, CUBLAS_COMPUTE_32F,
+        (long long)N * K, x, CUDA_R_16BF, x_ld, x_head_stride, &beta, out, CUDA_R_16BF, out_ld, out_head_stride, batch, CUBLAS_COMPUTE_32F,
         CUBLAS_GEMM_DEFAULT_TENSOR_OP);
     if (st != CUBLAS_STATUS_SUCCESS)
         throw KernelError("the library's batched matrix product failed with status " + std::to_string((int)st) + " for " + std::to_string(batch) +

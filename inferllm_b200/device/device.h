@@ -82,8 +82,11 @@ public:
     // (src/kern/gpu/kernel_gpu.cu:420-435).
     void library_gemm_bf16(const void* x, const void* w, void* out, DType out_dtype, int M, int N, int K);
     // `batch` products at once: out[:, b, :] = x[:, b, :] . w_b^T (transposed == false, w [batch * N, K]) or x[:, b, :] . w_b
-    // (transposed, w [batch * K, N]); x [M, batch * K] and out [M, batch * N] bfloat16 row-major.
-    void library_gemm_bf16_heads(const void* x, const void* w, void* out, int M, int N, int K, int batch, bool transposed);
+    // (transposed, w [batch * K, N]); x [M, batch * K] and out [M, batch * N] bfloat16 row-major.  With strides, a head's
+    // input or output is the head of a wider piece: rows x_ld / out_ld elements apart, heads x_head_stride / out_head_stride
+    // (0: the packed layout).
+    void library_gemm_bf16_heads(const void* x, const void* w, void* out, int M, int N, int K, int batch, bool transposed, int x_ld = 0,
+                                 long long x_head_stride = 0, int out_ld = 0, long long out_head_stride = 0);
 
     // Copy a small host array to the device without making the host wait for the work already queued:
     // through a ring of pinned staging buffers, each reused only when its copy has left.

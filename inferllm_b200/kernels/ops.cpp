@@ -470,10 +470,11 @@ Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepVi
     if (store) check_cache(kv, act_dtype, g, "qk_prep");
     if (p.rot_dim && !p.cos_sin) throw KernelError("qk_prep: a rotation needs its cos/sin table");
     Mat q = new_mat(dev, x.rows, (long long)g.n_heads * g.head_dim, act_dtype);
-    check_kernel(illm_qk_prep(x.p, code_of(x.dtype, "qk_prep"), (int)x.cols, p.q_off, has_kv ? p.k_off : -1, p.v_off, g.n_heads, g.n_kv_heads, g.head_dim, dv,
-                              p.q_bias, p.k_bias, p.v_bias, p.q_norm, p.k_norm, p.eps, p.cos_sin, p.rot_dim, p.pairs ? 1 : 0, (int)p.n_pos,
-                              ctx.token_pos, ctx.token_seq, kv.block_table, kv.width, kv.page_size, q.p, store ? kv.k : nullptr,
-                              store ? kv.v : nullptr, code_of(act_dtype, "qk_prep"), (int)x.rows, ctx.err, dev.stream()),
+    if (p.q_temp_every < 0) throw KernelError("qk_prep: the query temperature's period must not be negative");
+    check_kernel(illm_qk_prep_ex(x.p, code_of(x.dtype, "qk_prep"), (int)x.cols, p.q_off, has_kv ? p.k_off : -1, p.v_off, g.n_heads, g.n_kv_heads, g.head_dim, dv,
+                                 p.q_bias, p.k_bias, p.v_bias, p.q_norm, p.k_norm, p.eps, p.cos_sin, p.rot_dim, p.pairs ? 1 : 0, (int)p.n_pos,
+                                 ctx.token_pos, ctx.token_seq, kv.block_table, kv.width, kv.page_size, q.p, store ? kv.k : nullptr,
+                                 store ? kv.v : nullptr, code_of(act_dtype, "qk_prep"), (int)x.rows, ctx.err, p.q_temp_coef, p.q_temp_every, dev.stream()),
                  "qk_prep");
     return q;
 }
@@ -739,6 +740,23 @@ Mat attention_ex(Device& dev, const Mat& q, const KVView& kv, const StepView& ct
     return attention_generic(dev, q, kv, ctx, g, scale, &ex);
 }
 
+Mat attention_diff(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const DiffAttention& p) {
+    need(q, "q");
+    const int dv = kv.v_head_dim > 0 ? kv.v_head_dim : kv.head_dim;
+    if (g.n_kv_heads <= 0 || g.n_heads % g.n_kv_heads) throw KernelError("attention_diff: heads must be a multiple of kv heads");
+    if (g.head_dim <= 0 || g.head_dim > kMaxHeadDimGeneric || dv > kMaxHeadDimGeneric)
+        throw KernelError("attention_diff: a score map of " + std::to_string(g.head_dim) + " channels (values " + std::to_string(dv) +
+                          ") is not supported (up to " + std::to_string(kMaxHeadDimGeneric) + ")");
+    if (!kv.k || !kv.v || kv.dtype != q.dtype || kv.n_kv_heads != g.n_kv_heads || kv.head_dim != 2 * g.head_dim || q.cols < (long long)g.n_heads * 2 * g.head_dim)
+        throw KernelError("attention_diff: the cache entry must hold key rows of two maps (2 x " + std::to_string(g.head_dim) + " channels) in the queries' dtype");
+    Mat out = new_mat(dev, q.rows, (long long)g.n_heads * dv, q.dtype);
+    check_kernel(illm_attention_diff(q.p, (int)q.cols, kv.k, kv.v, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, code_of(q.dtype, "attention_diff"),
+                                     (int)q.rows, g.n_heads, g.n_kv_heads, g.head_dim, dv, kv.page_size, kv.window, scale, p.lambda, p.eps, p.out_scale,
+                                     dev.stream()),
+                 "attention_diff");
+    return out;
+}
+
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale) {
     const int nh = g.n_heads, nkv = g.n_kv_heads, d = g.head_dim, group = nkv ? nh / nkv : 0;
     // grids and scratch of the decode kernels are sized for the longest sequence the cache allows, so
@@ -765,6 +783,7 @@ int gate_act_from_name(const std::string& name) {
     if (name == "silu") return kActSilu;
     if (name == "relu") return kActRelu;
     if (name == "gelu_tanh") return kActGeluTanh;
+    if (name == "swish_clamped") return kActSwishClamped;
     return -1;
 }
 
@@ -781,6 +800,28 @@ Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, co
                                    code_of(out_dtype, "add2_rmsnorm"), (int)resid.rows, (int)resid.cols, eps, dev.stream()),
                  "add2_rmsnorm");
     return y;
+}
+
+Mat scaled_add_rmsnorm(Device& dev, const Mat& resid, const Mat& delta, const float* bias, const float* ls, const Mat* w, float eps, DType out_dtype) {
+    need(resid, "resid", true, DType::F32);
+    need(delta, "delta", true, DType::F32);
+    if (w) need(*w, "norm weight", true, DType::F32);
+    if (!ls) throw KernelError("scaled_add_rmsnorm: no layer scale");
+    if (delta.rows != resid.rows || delta.cols != resid.cols || (w && w->rows * w->cols != resid.cols))
+        throw KernelError("scaled_add_rmsnorm: the addition and the weight must have the stream's shape");
+    if (resid.cols > kMaxNormWidth) throw KernelError("scaled_add_rmsnorm: width " + std::to_string(resid.cols) + " exceeds what one block's shared memory holds");
+    Mat y;
+    if (w) y = new_mat(dev, resid.rows, resid.cols, out_dtype);
+    check_kernel(illm_scaled_add_rmsnorm((float*)resid.p, (const float*)delta.p, bias, ls, w ? (const float*)w->p : nullptr, y.p,
+                                         code_of(out_dtype, "scaled_add_rmsnorm"), (int)resid.rows, (int)resid.cols, eps, dev.stream()),
+                 "scaled_add_rmsnorm");
+    return y;
+}
+
+void add_bias(Device& dev, const Mat& y, const float* bias) {
+    need(y, "y");
+    if (!bias) throw KernelError("add_bias: no bias");
+    check_kernel(illm_add_bias(y.p, code_of(y.dtype, "add_bias"), bias, (int)y.rows, (int)y.cols, dev.stream()), "add_bias");
 }
 
 Mat take_columns(Device& dev, const Mat& x, long long off, long long n, DType dtype) {
@@ -855,43 +896,81 @@ Mat latent_prep(Device& dev, const Mat& x, int q_rank, int kv_rank, const float*
     return cq;
 }
 
-Mat latent_attention_any(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, int heads, float scale) {
+Mat latent_attention_any(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, int heads, float scale, const float* gate, int gate_stride) {
     need(q, "q");
     if (!kv.k || kv.n_kv_heads != 1 || kv.dtype != q.dtype || q.cols != (long long)heads * kv.head_dim)
         throw KernelError("latent_attention_any: the queries and the cache entry (one head, the queries' dtype) do not fit together");
     Mat out = new_mat(dev, q.rows, q.cols, q.dtype);
-    const int rc = illm_latent_attention_any(q.p, kv.k, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, code_of(q.dtype, "latent_attention_any"),
-                                             (int)q.rows, heads, kv.head_dim, kv.page_size, kv.window, scale, dev.stream());
+    const int rc = illm_latent_attention_any_gated(q.p, kv.k, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, code_of(q.dtype, "latent_attention_any"),
+                                                   (int)q.rows, heads, kv.head_dim, kv.page_size, kv.window, scale, gate, gate_stride, dev.stream());
     if (rc == 10001) throw KernelError("latent_attention_any: a latent of " + std::to_string(kv.head_dim) + " channels is beyond the kernel (up to 1024)");
     check_kernel(rc, "latent_attention_any");
     return out;
 }
 
 Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype) {
+    return head_linear_pieces(dev, x, w, heads, transposed, out_dtype, HeadPieces());
+}
+
+Mat head_linear_pieces(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype, const HeadPieces& pc) {
     need(x, "x");
     need(w, "w");
     if (heads <= 0 || x.cols % heads) throw KernelError("head_linear: the input's width is not a multiple of the head count");
-    const long long K = x.cols / heads;
-    long long N;
+    const long long x_hs = x.cols / heads;
+    if (pc.x_head_stride && pc.x_head_stride != x_hs) throw KernelError("head_linear: the input's width is not heads x the given piece");
+    long long K, N;
     if (transposed) {
-        if (w.rows != (long long)heads * K) throw KernelError("head_linear: the matrix must have heads * n_in rows");
+        if (w.rows % heads) throw KernelError("head_linear: the matrix must have heads * n_in rows");
+        K = w.rows / heads;
         N = w.cols;
     } else {
-        if (w.cols != K || w.rows % heads) throw KernelError("head_linear: the matrix must be [heads * n_out, n_in]");
+        if (w.rows % heads) throw KernelError("head_linear: the matrix must be [heads * n_out, n_in]");
+        K = w.cols;
         N = w.rows / heads;
     }
-    Mat y = new_mat(dev, x.rows, (long long)heads * N, out_dtype);
+    if (K > x_hs || (!pc.x_head_stride && K != x_hs)) throw KernelError("head_linear: the matrix does not fit the input's heads");
+    Mat y;
+    long long y_hs = N;
+    if (pc.into) {
+        y = *pc.into;
+        y_hs = pc.y_head_stride;
+        if (!y.p || y.dtype != out_dtype || y.rows != x.rows || y_hs < N || y.cols != heads * y_hs)
+            throw KernelError("head_linear: the matrix to write into must be [T, heads x its piece] of the output dtype");
+    } else {
+        y = new_mat(dev, x.rows, (long long)heads * N, out_dtype);
+    }
     // prompts in bfloat16: the library's batched product (a head per batch entry); few rows and float32: the kernel here
     if (x.dtype == DType::BF16 && w.dtype == DType::BF16 && out_dtype == DType::BF16 && x.rows > kGemmTcMaxTokensAuto && K % 8 == 0 && N % 8 == 0 &&
-        !((uintptr_t)x.p & 15) && !((uintptr_t)w.p & 15)) {
-        dev.library_gemm_bf16_heads(x.p, w.p, y.p, (int)x.rows, (int)N, (int)K, heads, transposed);
+        x_hs % 8 == 0 && y_hs % 8 == 0 && !((uintptr_t)x.p & 15) && !((uintptr_t)w.p & 15) && !((uintptr_t)y.p & 15)) {
+        dev.library_gemm_bf16_heads(x.p, w.p, y.p, (int)x.rows, (int)N, (int)K, heads, transposed, (int)x.cols, x_hs, (int)y.cols, y_hs);
         return y;
     }
-    const int rc = illm_head_gemm(x.p, code_of(x.dtype, "head_linear"), w.p, code_of(w.dtype, "head_linear"), y.p, code_of(out_dtype, "head_linear"),
-                                  (int)x.rows, heads, (int)N, (int)K, transposed ? 1 : 0, dev.stream());
-    if (rc == 10001) throw KernelError("head_linear: this combination of dtypes is not supported");
+    const int rc = illm_head_gemm_ex(x.p, code_of(x.dtype, "head_linear"), w.p, code_of(w.dtype, "head_linear"), y.p, code_of(out_dtype, "head_linear"),
+                                     (int)x.rows, heads, (int)N, (int)K, transposed ? 1 : 0, (int)x.cols, (int)x_hs, (int)y.cols, (int)y_hs, dev.stream());
+    if (rc == 10001) throw KernelError("head_linear: this combination of dtypes and sizes is not supported");
     check_kernel(rc, "head_linear");
     return y;
+}
+
+Mat latent_rope_prep(Device& dev, const Mat& x, const LatentRope& p, const StepView& ctx, const KVView& kv, DType act_dtype, Mat* qa) {
+    need(x, "the packed latent projection", true, DType::F32);
+    const long long row = (long long)p.kv_rank + p.rot_head_dim;
+    if (p.n_heads <= 0 || p.head_dim <= 0 || p.rot_head_dim < 0 || p.kv_rank <= 0 || p.q_off < 0 || p.c_off < 0 ||
+        p.q_off + (long long)p.n_heads * (p.head_dim + p.rot_head_dim) > x.cols || p.c_off + row > x.cols)
+        throw KernelError("latent_rope_prep: the projection is narrower than the queries and the latent");
+    if (p.rot_dim && !p.cos_sin) throw KernelError("latent_rope_prep: a rotation needs its cos/sin table");
+    if (kv.writes && (!kv.k || kv.dtype != act_dtype || kv.n_kv_heads != 1 || kv.head_dim != row))
+        throw KernelError("latent_rope_prep: the cache entry must hold one head of kv_rank + rotated channels in the activation dtype");
+    if (!qa) throw KernelError("latent_rope_prep: nowhere to put the absorbed queries");
+    *qa = new_mat(dev, x.rows, p.n_heads * row, act_dtype);
+    const bool q_f32 = ctx.is_decode || act_dtype == DType::F32;
+    Mat qn = new_mat(dev, x.rows, (long long)p.n_heads * p.head_dim, q_f32 ? DType::F32 : act_dtype);
+    check_kernel(illm_latent_rope_prep((const float*)x.p, (int)x.cols, p.q_off, p.n_heads, p.head_dim, p.rot_head_dim, p.c_off, p.kv_rank, p.w_kv, p.eps,
+                                       p.cos_sin, p.rot_dim, p.pairs ? 1 : 0, (int)p.n_pos, ctx.token_pos, ctx.token_seq, kv.block_table, kv.width,
+                                       kv.page_size, qn.p, q_f32 ? 1 : 0, qa->p, kv.writes ? kv.k : nullptr, code_of(act_dtype, "latent_rope_prep"),
+                                       (int)x.rows, ctx.err, dev.stream()),
+                 "latent_rope_prep");
+    return qn;
 }
 
 Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* router_bias, int E, int top, const Mat& w_gu, const Mat& w_down, int act) {
@@ -922,25 +1001,27 @@ Mat moe_forward_ex(Device& dev, const Mat& h, const Mat& logits, const MoeRoutin
     int* tile_expert = dev.alloc_n<int>((size_t)tiles);
     int* tile_row0 = dev.alloc_n<int>((size_t)tiles);
     int* tile_rows = dev.alloc_n<int>((size_t)tiles);
-    if (r.scoring == 1 && (r.groups < 1 || r.groups > 32 || E % r.groups || r.keep < 1 || r.keep > r.groups || (long long)r.keep * (E / r.groups) < top))
+    if (r.scoring >= 1 && (r.groups < 1 || r.groups > 32 || E % r.groups || r.keep < 1 || r.keep > r.groups || (long long)r.keep * (E / r.groups) < top))
         throw KernelError("moe: the experts must form up to 32 equal groups, and the groups kept must hold at least `top` experts");
     if (r.plus && (r.plus->dtype != DType::F32 || r.plus->rows != T || r.plus->cols != D)) throw KernelError("moe: the addend must be float32 [T, hidden]");
-    check_kernel(illm_moe_route_ex((const float*)logits.p, r.bias, (int)T, E, top, bm, r.scoring, r.groups, r.keep, r.renorm ? 1 : 0, expert, weight, row_of_pair,
-                                   pair_of_row, tile_expert, tile_row0, tile_rows, dev.stream()),
+    if (r.scoring < 0 || r.scoring > 2 || r.group_top < 1 || r.group_top > 4) throw KernelError("moe: unknown scoring, or a group score of more than 4 experts");
+    if (act == kActSwishClamped && !(r.act_limit > 0.f)) throw KernelError("moe: the clamped activation needs a positive limit");
+    check_kernel(illm_moe_route_ex2((const float*)logits.p, r.bias, (int)T, E, top, bm, r.scoring, r.groups, r.keep, r.renorm ? 1 : 0, r.group_top, r.sum_eps,
+                                    r.weight_scale, expert, weight, row_of_pair, pair_of_row, tile_expert, tile_row0, tile_rows, dev.stream()),
                  "moe_route");
     const int code = code_of(h.dtype, "moe");
     Mat hid = new_mat_exact(dev, P, F, h.dtype), rows = new_mat_exact(dev, P, D, DType::F32), out = new_mat_exact(dev, T, D, DType::F32);
     if (tc5) {
         Mat xs = new_mat_exact(dev, P, D, DType::BF16);
         check_kernel(illm_moe_gather_rows(h.p, xs.p, pair_of_row, (int)P, (int)D, top, dev.stream()), "moe_gather_rows");
-        check_kernel(illm_moe_gemm_tc(xs.p, w_gu.p, hid.p, (int)P, E, (int)(2 * F), (int)D, 1, act, tiles, tile_expert, tile_row0, tile_rows,
+        check_kernel(illm_moe_gemm_tc_ex(xs.p, w_gu.p, hid.p, (int)P, E, (int)(2 * F), (int)D, 1, act, r.act_limit, tiles, tile_expert, tile_row0, tile_rows,
                                       dev.tc_error_word(), dev.stream()),
                      "moe_gemm_tc (gate/up)");
         check_kernel(illm_moe_gemm_tc(hid.p, w_down.p, rows.p, (int)P, E, (int)D, (int)F, 0, 0, tiles, tile_expert, tile_row0, tile_rows,
                                       dev.tc_error_word(), dev.stream()),
                      "moe_gemm_tc (down)");
     } else {
-        check_kernel(illm_moe_gemm(h.p, code, w_gu.p, code, hid.p, (int)T, top, E, (int)(2 * F), (int)D, 1, act, bm, tc, pair_of_row, tile_expert, tile_row0,
+        check_kernel(illm_moe_gemm_ex(h.p, code, w_gu.p, code, hid.p, (int)T, top, E, (int)(2 * F), (int)D, 1, act, r.act_limit, bm, tc, pair_of_row, tile_expert, tile_row0,
                                    tile_rows, dev.stream()),
                      "moe_gemm (gate/up)");
         check_kernel(illm_moe_gemm(hid.p, code, w_down.p, code, rows.p, (int)T, top, E, (int)D, (int)F, 0, 0, bm, tc, pair_of_row, tile_expert, tile_row0,

@@ -200,6 +200,14 @@ struct MixedAttention {
 };
 bool attention_mixed_supported(DType dtype, int nh, int nkv, int d);
 Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const MixedAttention& m);
+// Differential attention (csrc/attention_diff.cu): every head has two score maps over the same values.  q [T, heads * 2 d]
+// (a head's row is [q_1, q_2]), the cache entry's key rows [k_1, k_2] (kv.head_dim == 2 d) and value rows of
+// kv.v_head_dim; o = a_1 - lambda a_2, divided by its root mean square over the head's values (eps inside the root), times
+// out_scale.  g.head_dim is d, the size of ONE map.  Returns [T, heads * v_head_dim] in q's dtype.
+struct DiffAttention {
+    float lambda = 0.f, eps = 1e-6f, out_scale = 1.f;
+};
+Mat attention_diff(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const DiffAttention& p);
 // Attention of the step's tokens over a cache entry: picks the kernel for the dtype, head size and kind of step.
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
 
@@ -222,6 +230,10 @@ struct QkPrep {
     int rot_dim = 0;
     bool pairs = false;
     long long n_pos = 0;
+    // a temperature on the queries that grows with the position p: q *= 1 + q_temp_coef * ln((p + 1) / q_temp_every + 1)
+    // (whole-numbered division), behind the bias; q_temp_every 0: none
+    float q_temp_coef = 0.f;
+    int q_temp_every = 0;
 };
 Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepView& ctx, const KVView& kv, DType act_dtype);
 
@@ -291,10 +303,18 @@ Mat group_norm_gate(Device& dev, const Mat& o_f32, int group, const float* w, fl
 // ---- pieces of further mixers, feed-forwards and embeddings
 
 // Activations of the gated feed-forward: act(gate) * up.
-enum GateAct { kActSilu = 1, kActRelu = 2, kActGeluTanh = 3 };
+// kActSwishClamped (routed experts only): g = min(gate, limit), u = clamp(up, -limit, limit); g sigmoid(1.702 g) (u + 1)
+enum GateAct { kActSilu = 1, kActRelu = 2, kActGeluTanh = 3, kActSwishClamped = 4 };
 int gate_act_from_name(const std::string& name);        // ConfigError-free: -1 for an unknown name
 // resid += d1 (+ d2), all float32 [T, H], and the RMS norm of the new rows times w (float32 [H]) in `out_dtype`: one kernel
 Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, const Mat& weight_f32, float eps, DType out_dtype);
+// resid += (delta (+ bias)) * ls, all float32 (bias, ls float32 [H] on the device; bias may be nullptr), and, with a weight,
+// the RMS norm of the new rows times w (float32 [H]) in `out_dtype`: a sublayer's output through a per-channel layer scale,
+// folded into the next norm.  Without a weight an empty matrix comes back.
+Mat scaled_add_rmsnorm(Device& dev, const Mat& resid, const Mat& delta_f32, const float* bias, const float* ls, const Mat* weight_f32, float eps,
+                       DType out_dtype);
+// y[t, :] += bias (float32 [cols] on the device), in place
+void add_bias(Device& dev, const Mat& y, const float* bias);
 // columns [off, off + n) of a float32 matrix as a contiguous matrix of `dtype`
 Mat take_columns(Device& dev, const Mat& x_f32, long long off, long long n, DType dtype);
 // [a, b] row by row (two float32 matrices of equal shape) as a matrix of `dtype`
@@ -325,20 +345,47 @@ Mat latent_prep(Device& dev, const Mat& x_f32, int q_rank, int kv_rank, const fl
                 const KVView& kv, DType act_dtype);
 // Attention of `heads` query heads over one shared key/value head of ANY width (a keys-only cache entry), float32 math:
 // for widths the framework's attention kernels do not take.  q [T, heads * width] in the cache's dtype.
-Mat latent_attention_any(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, int heads, float scale);
+// gate (float32 [T, gate_stride] or nullptr): head h of token t is multiplied by sigmoid(gate[t * gate_stride + h])
+Mat latent_attention_any(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, int heads, float scale, const float* gate = nullptr,
+                         int gate_stride = 0);
 // y[t, h, :] = W_h x[t, h, :] (transposed = false, w [heads * n_out, n_in]) or W_h^T x[t, h, :] (w [heads * n_in, n_out])
 Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype);
+// The same where a head's input is the first n_in channels of a wider piece of x (x [T, heads * x_head_stride]) and/or its
+// output goes to the first n_out channels of a wider piece of an existing matrix `into` ([T, heads * y_head_stride]).
+struct HeadPieces {
+    long long x_head_stride = 0;      // 0: n_in
+    Mat* into = nullptr;              // nullptr: a new [T, heads * n_out] matrix
+    long long y_head_stride = 0;      // with `into`
+};
+Mat head_linear_pieces(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype, const HeadPieces& pc);
+// The step between the packed projection and attention of a latent-attention layer with rotated channels
+// (latent_rope_prep_kernel, csrc/latent_attention.cu).  x_f32: the packed projection with the queries (heads x (d + dr)) at
+// q_off and [latent (kv_rank), raw shared key part (dr)] at c_off.  Writes the cache row [normed latent, rotated key part],
+// returns q_nope [T, heads * d] (float32 for single tokens, else the activation dtype) and fills the last dr channels per
+// head of qa [T, heads * (kv_rank + dr)] (activation dtype) with the rotated query parts.
+struct LatentRope {
+    int q_off = 0, c_off = 0, n_heads = 0, head_dim = 0, rot_head_dim = 0, kv_rank = 0;
+    const float* w_kv = nullptr;
+    float eps = 1e-6f;
+    const float* cos_sin = nullptr;
+    int rot_dim = 0;
+    bool pairs = true;
+    long long n_pos = 0;
+};
+Mat latent_rope_prep(Device& dev, const Mat& x_f32, const LatentRope& p, const StepView& ctx, const KVView& kv, DType act_dtype, Mat* qa);
 
 // Routed feed-forward (csrc/moe.cu).  logits float32 [T, experts] without the bias.  w_gate_up [experts * 2 ff, hidden]
 // (per expert, rows 2i and 2i + 1 are gate and up of output i), w_down [experts * hidden, ff].  Returns float32 [T, hidden].
 Mat moe_forward(Device& dev, const Mat& h, const Mat& logits_f32, const float* router_bias, int experts, int top, const Mat& w_gate_up,
                 const Mat& w_down, int act);
 // How the experts are chosen and weighted.  scoring 0: the largest logits (+ bias), weights the softmax over the chosen;
-// scoring 1: scores are the softmax over all experts, `bias` enters the choice only, the experts form `groups` equal
-// groups of neighbours of which the `keep` best (by their largest choice score) may be chosen from, and the weights
-// are the chosen scores, divided by their sum only if `renorm`.  plus: float32 [T, hidden] added to the result.
+// scoring 1: scores are the softmax over all experts (2: the sigmoid of every logit), `bias` enters the choice only, the
+// experts form `groups` equal groups of neighbours of which the `keep` best (by the sum of their `group_top` largest choice
+// scores) may be chosen from, and the weights are the chosen scores, divided by their sum (+ sum_eps) only if `renorm`,
+// then times weight_scale.  plus: float32 [T, hidden] added to the result.  act_limit: the limit of kActSwishClamped.
 struct MoeRouting {
-    int scoring = 0, groups = 1, keep = 1;
+    int scoring = 0, groups = 1, keep = 1, group_top = 1;
+    float sum_eps = 0.f, weight_scale = 1.f, act_limit = 0.f;
     bool renorm = true;
     const float* bias = nullptr;
     const Mat* plus = nullptr;

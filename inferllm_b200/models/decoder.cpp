@@ -32,7 +32,8 @@ DecoderModel::DecoderModel(const ModelSpec& s, Runtime* runtime) : spec(s), rt(r
     }
     final_norm_ = build_norm(spec.final_norm, rt);
     head_ = build_head(spec.head, rt);
-    if (!spec.reentry.kind.empty()) reentry_ = build_feed_forward(spec.reentry, rt);
+    // "add_embedding" is no part: the embedding output itself is added to the stream
+    if (!spec.reentry.kind.empty() && spec.reentry.kind != kReentryAddEmbedding) reentry_ = build_feed_forward(spec.reentry, rt);
 }
 
 std::vector<std::pair<std::string, Part*>> DecoderModel::owners() const {
@@ -93,7 +94,8 @@ Mat DecoderModel::forward(const StepContext& ctx, const SequenceCache& cache, co
         stream = embedding_->forward(ctx);
     }
     Mat x0;      // the embedding output, kept for the entries that re-enter the stream
-    if (reentry_) {
+    const bool reenters = !spec.reentry.kind.empty();
+    if (reenters) {
         stream.flush();
         x0 = stream.x;
         x0.p = dev.alloc(x0.bytes());
@@ -104,7 +106,13 @@ Mat DecoderModel::forward(const StepContext& ctx, const SequenceCache& cache, co
         // the layers' activations take turns in two lanes of the step arena: what a layer leaves for the
         // next one (its last output, pending in the stream) is read before this lane's turn comes again
         dev.set_lane(1 + (turn++ & 1), true);
-        if (e.reenter) {
+        if (e.reenter && !reentry_) {
+            // x <- x + x0, in float32
+            stream.flush();
+            MatOrPartials again;
+            again.m = x0;
+            ops::residual_add(dev, stream.x, again);
+        } else if (e.reenter) {
             // x <- W [x; x0]; the result goes back into the stream's own rows, which outlive the lanes
             stream.flush();
             MatOrPartials y = reentry_->forward(ops::join_rows(dev, stream.x, x0, rt->dtype), ctx, false);

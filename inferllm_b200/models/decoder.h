@@ -20,6 +20,9 @@ class SequenceCache;
 
 // The cache entry number of an embedding that keeps per-sequence state (schedule entries count from 0).
 constexpr int kEmbeddingCacheEntry = -1;
+// ModelSpec::reentry of this kind is no part: before a schedule entry marked `reenter` the embedding output is added to
+// the stream (x <- x + x0, float32), instead of a map of the two joined.
+constexpr const char* kReentryAddEmbedding = "add_embedding";
 // A mixer's second entry (Mixer::aux_cache_request) has the number of its first plus this.
 constexpr int kAuxCacheEntryBase = 1 << 20;
 

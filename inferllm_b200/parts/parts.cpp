@@ -226,6 +226,18 @@ struct RMSNorm : Norm {
         return ops::scale_add_rmsnorm(*rt->dev, stream.x, d, weight.m, residual_scale, eps, rt->dtype);
     }
     Mat forward(ResidualStream& stream, const int* rows, long long n_rows) override {
+        // an addition that passes a layer scale on its way into the stream: x + factors * pending and the norm in one kernel
+        if (stream.has_pending && stream.pending_post) {
+            const Mat* ls = stream.pending_post->channel_scale();
+            if (ls && rows == nullptr && !stream.has_pending2 && !stream.pending.is_partials() && stream.pending.m.dtype == DType::F32 &&
+                weight.m.dtype == DType::F32) {
+                Mat y = ops::scaled_add_rmsnorm(*rt->dev, stream.x, stream.pending.m, nullptr, (const float*)ls->p, &weight.m, eps, rt->dtype);
+                stream.has_pending = false;
+                stream.pending_post = nullptr;
+                return y;
+            }
+            stream.flush();
+        }
         // float32 additions (one or two finished matrices) fold into one kernel with the norm; what that kernel does not
         // take (a second addition otherwise, a float32 addition beside a 16-bit output, gathered rows) is added first
         const bool f32_pending = stream.has_pending && !stream.pending.is_partials() && stream.pending.m.dtype == DType::F32;
@@ -240,6 +252,27 @@ struct RMSNorm : Norm {
                                  rows == nullptr);
         if (rows == nullptr) stream.has_pending = false;
         return y;
+    }
+};
+
+// "layer_scale": a learned factor per channel on a sublayer's output before it joins the stream, x <- x + s * f(..).  It
+// stands where a block puts a norm behind a sublayer (ResidualStream::add_normed); the next RMS norm folds it into its
+// own kernel (channel_scale), flush() applies it alone.  `tensor`: the factors' name below the part's prefix.
+struct LayerScale : Norm {
+    long long size;
+    std::string tensor;
+    OwnedMat factors;
+    LayerScale(const PartSpec& s, Runtime* rt) : Norm(s, rt), size(s.get_int("size")), tensor(s.get_string("tensor", "weight")) {
+        if (size <= 0) throw ConfigError("layer_scale: size must be positive");
+    }
+    TensorDecls tensors() const override { return {{tensor, TensorDecl{{size}, "norm"}}}; }
+    void load(TensorSource& src) override { factors = fetch_owned(rt, src, tensor, DType::F32, "a layer scale"); }
+    const Mat* channel_scale() const override { return &factors.m; }
+    Mat forward(ResidualStream&, const int*, long long) override { throw EngineError("layer_scale: stands behind a sublayer, not in front of one"); }
+    void add_normed_pending(ResidualStream& stream) override {
+        Mat y = stream.pending.is_partials() ? ops::materialize(*rt->dev, stream.pending.part, DType::F32) : ops::cast(*rt->dev, stream.pending.m, DType::F32);
+        ops::scaled_add_rmsnorm(*rt->dev, stream.x, y, nullptr, (const float*)factors.m.p, nullptr, 0.f, DType::F32);
+        stream.has_pending = false;
     }
 };
 
@@ -347,17 +380,28 @@ struct NoPosition : PositionEncoding {
 // score_h <- sum_g M[h, g] score_g, tensor "mix" [heads, heads]) and `out_gate` = "sigmoid" (a full-width gate
 // projection of the mixer's input; the concatenated heads are multiplied by its sigmoid element by element).  The
 // last three need the first.
+//
+// A third family: `score_maps` = 2 (differential attention: a head's query row is [q_1, q_2] and a key head's row
+// [k_1, k_2], `head_dim` the size of ONE map; both maps are softmax attentions of their own over the same values and
+// o = a_1 - lambda a_2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + `diff`, four vectors of head_dim entries and one
+// number for the layer, made once at load; then o / sqrt(mean(o^2) + norm_eps) over the head's values, times 1 - diff;
+// ops::attention_diff), `q_temperature` {coef, every} (the queries of position p are multiplied by
+// 1 + coef ln(floor((p + 1) / every) + 1), behind the bias) and `o_bias` (a bias on the output projection).
 struct Attention : Mixer {
     long long hidden;
     int n_heads, n_kv_heads, head_dim, v_head_dim, window;
     float scale, norm_eps;
     bool qkv_bias, proj_norm, has_sink, has_gate, own_kv, out_f32;
     bool values_are_keys, log_distance, head_mix, wide_gate;
+    int maps = 1;                     // score maps per head (2: differential attention)
+    bool o_bias = false;
+    float diff = 0.f, lambda = 0.f, q_temp_coef = 0.f;
+    int q_temp_every = 0;
     std::map<std::string, std::string> names;
     std::unique_ptr<PositionEncoding> position;
     DeviceBuffer qkv_buf, o_buf;
     Mat w_qkv, w_o;
-    OwnedMat b_q, b_k, b_v, n_q, n_k, sinks, dist_r1, dist_r2, mix;
+    OwnedMat b_q, b_k, b_v, b_o, n_q, n_k, sinks, dist_r1, dist_r2, mix;
     Attention(const PartSpec& s, Runtime* rt)
             : Mixer(s, rt), hidden(s.get_int("hidden_size")), n_heads((int)s.get_int("n_heads")), n_kv_heads((int)s.get_int("n_kv_heads")),
               head_dim((int)s.get_int("head_dim")), v_head_dim((int)s.get_int("v_head_dim", s.get_int("head_dim"))),
@@ -381,12 +425,29 @@ struct Attention : Mixer {
             throw ConfigError("attention: distance_bias, head_mix and the element-wise gate run on the kernel for values = keys only");
         if (values_are_keys && (v_head_dim != head_dim || !own_kv || qkv_bias || proj_norm || has_sink || has_gate))
             throw ConfigError("attention: values = keys needs key and value heads of one size and takes no biases, projection norms, sinks or head gates");
+        maps = (int)s.get_int("score_maps", 1);
+        o_bias = s.get_bool("o_bias", false);
+        if (maps != 1 && maps != 2) throw ConfigError("attention: score_maps must be 1 or 2");
+        if (maps == 2) {
+            diff = (float)s.get_double("diff");
+            if (values_are_keys || has_sink || has_gate || !own_kv)
+                throw ConfigError("attention: two score maps take no sinks and no head gates, and need keys and values of their own");
+        }
+        if (s.has("q_temperature")) {
+            const Json& qt = s.params.at("q_temperature");
+            if (!qt.is_object() || !qt.has("coef") || !qt.has("every") || !qt.at("coef").is_number() || !qt.at("every").is_int() || qt.at("every").as_int() < 1)
+                throw ConfigError("attention: q_temperature must be {coef, every} with every >= 1");
+            if (values_are_keys) throw ConfigError("attention: values = keys takes no query temperature");
+            q_temp_coef = (float)qt.at("coef").as_double();
+            q_temp_every = (int)qt.at("every").as_int();
+        }
         if (rt && values_are_keys && !ops::attention_mixed_supported(rt->dtype, n_heads, n_kv_heads, head_dim))
             throw ConfigError("attention: " + std::to_string(n_heads) + " heads of " + std::to_string(head_dim) +
                               " channels are beyond the kernel for mixed scores (heads x head size up to 8192)");
         names = {{"q", "q_proj.weight"}, {"k", "k_proj.weight"}, {"v", "v_proj.weight"}, {"o", "o_proj.weight"},
                  {"q_bias", "q_proj.bias"}, {"k_bias", "k_proj.bias"}, {"v_bias", "v_proj.bias"}, {"q_norm", "q_norm.weight"},
-                 {"k_norm", "k_norm.weight"}, {"sink", "sinks"}, {"gate", "gate_proj.weight"}, {"r1", "r1"}, {"r2", "r2"}, {"mix", "mix"}};
+                 {"k_norm", "k_norm.weight"}, {"sink", "sinks"}, {"gate", "gate_proj.weight"}, {"r1", "r1"}, {"r2", "r2"}, {"mix", "mix"},
+                 {"o_bias", "o_proj.bias"}, {"lq1", "lambda_q1"}, {"lk1", "lambda_k1"}, {"lq2", "lambda_q2"}, {"lk2", "lambda_k2"}};
         if (s.has("names"))
             for (auto& m : s.params.at("names").members()) names[m.first] = m.second.as_string();
         // the attention kernels read heads 16 bytes at a time: said when the model is built, not at its first step
@@ -402,7 +463,7 @@ struct Attention : Mixer {
     }
     // true if the layer needs the general path (see above)
     bool general() const {
-        return v_head_dim != head_dim || qkv_bias || proj_norm || has_sink || has_gate || !own_kv || out_f32;
+        return v_head_dim != head_dim || qkv_bias || proj_norm || has_sink || has_gate || !own_kv || out_f32 || maps == 2 || q_temp_every > 0 || o_bias;
     }
     long long gate_rows() const { return has_gate ? n_heads : wide_gate ? (long long)n_heads * v_head_dim : 0; }
     bool graph_safe() const override { return true; }     // a decode step's launches depend only on the batch size
@@ -416,7 +477,7 @@ struct Attention : Mixer {
         return window == 0 && !values_are_keys && position->rotation_table(&t, &rot, &n);
     }
     TensorDecls tensors() const override {
-        const long long q = (long long)n_heads * head_dim, k = (long long)n_kv_heads * head_dim, v = (long long)n_kv_heads * v_head_dim;
+        const long long q = (long long)n_heads * maps * head_dim, k = (long long)n_kv_heads * maps * head_dim, v = (long long)n_kv_heads * v_head_dim;
         const long long o = (long long)n_heads * v_head_dim;
         TensorDecls d;
         auto nm = [&](const char* role) { return names.at(role); };
@@ -439,12 +500,15 @@ struct Attention : Mixer {
             d.push_back({nm("r2"), TensorDecl{{(long long)n_heads}}});
         }
         if (head_mix) d.push_back({nm("mix"), TensorDecl{{(long long)n_heads, (long long)n_heads}}});
+        if (maps == 2)
+            for (const char* role : {"lq1", "lk1", "lq2", "lk2"}) d.push_back({nm(role), TensorDecl{{(long long)head_dim}}});
         d.push_back({nm("o"), TensorDecl{{hidden, o}}});
+        if (o_bias) d.push_back({nm("o_bias"), TensorDecl{{hidden}}});
         return d;
     }
     // rows of the packed matrix: q, then k and v (a layer with keys and values of its own), then the gate
-    long long q_rows() const { return (long long)n_heads * head_dim; }
-    long long k_rows() const { return own_kv ? (long long)n_kv_heads * head_dim : 0; }
+    long long q_rows() const { return (long long)n_heads * maps * head_dim; }
+    long long k_rows() const { return own_kv ? (long long)n_kv_heads * maps * head_dim : 0; }
     long long v_rows() const { return own_kv && !values_are_keys ? (long long)n_kv_heads * v_head_dim : 0; }
     long long packed_rows() const { return q_rows() + k_rows() + v_rows() + gate_rows(); }
     void load(TensorSource& src) override {
@@ -480,10 +544,28 @@ struct Attention : Mixer {
             dist_r2 = fetch_owned(rt, src, names.at("r2"), DType::F32, "an attention layer's distance factors");
         }
         if (head_mix) mix = fetch_owned(rt, src, names.at("mix"), DType::F32, "an attention layer's head-mixing matrix");
+        if (o_bias) b_o = fetch_owned(rt, src, names.at("o_bias"), DType::F32, "an attention bias");
+        if (maps == 2) {
+            // lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff: one number for the layer, made once in float32
+            std::vector<float> v[4];
+            const char* roles[4] = {"lq1", "lk1", "lq2", "lk2"};
+            for (int i = 0; i < 4; i++) {
+                OwnedMat t = fetch_owned(rt, src, names.at(roles[i]), DType::F32, "a lambda vector");
+                v[i].resize((size_t)head_dim);
+                rt->dev->synchronize();
+                check_cuda(cudaMemcpy(v[i].data(), t.m.p, v[i].size() * sizeof(float), cudaMemcpyDeviceToHost), "reading a lambda vector");
+            }
+            float d1 = 0.f, d2 = 0.f;
+            for (int c = 0; c < head_dim; c++) {
+                d1 = std::fmaf(v[0][c], v[1][c], d1);
+                d2 = std::fmaf(v[2][c], v[3][c], d2);
+            }
+            lambda = std::exp(d1) - std::exp(d2) + diff;
+        }
     }
     CacheRequest cache_request() const override {
         if (values_are_keys) return CacheRequest::paged_keys_only(n_kv_heads, head_dim, window);
-        return own_kv ? CacheRequest::paged(n_kv_heads, head_dim, window, v_head_dim) : CacheRequest();
+        return own_kv ? CacheRequest::paged(n_kv_heads, maps * head_dim, window, v_head_dim) : CacheRequest();
     }
 
     // values = keys: one float32 product for q, k and the gate; q out and k into the pages (with the table rotation,
@@ -521,8 +603,8 @@ struct Attention : Mixer {
 
     MatOrPartials forward_general(const Mat& h, const StepContext& ctx, KVView kv, bool may_defer) {
         Device& dev = *rt->dev;
-        const ops::Geometry g{n_heads, n_kv_heads, head_dim};
-        if (kv.n_kv_heads != n_kv_heads || kv.head_dim != head_dim || (kv.v_head_dim > 0 ? kv.v_head_dim : kv.head_dim) != v_head_dim)
+        const ops::Geometry g{n_heads, n_kv_heads, maps * head_dim};      // with two maps a head's row is [map 1, map 2]
+        if (kv.n_kv_heads != n_kv_heads || kv.head_dim != maps * head_dim || (kv.v_head_dim > 0 ? kv.v_head_dim : kv.head_dim) != v_head_dim)
             throw EngineError("attention: the cache entry's keys and values do not have this layer's head count and sizes");
         if (!own_kv && kv.writes) throw EngineError("attention: a layer without key and value projections cannot write a cache entry");
         Mat x = ops::linear(dev, rt->gemm, h, w_qkv, DType::F32, false).m;
@@ -548,7 +630,17 @@ struct Attention : Mixer {
         p.rot_dim = rot;
         p.pairs = pairs;
         p.n_pos = n_pos;
+        p.q_temp_coef = q_temp_coef;
+        p.q_temp_every = q_temp_every;
         Mat q = ops::qk_prep(dev, x, p, g, ctx, kv, rt->dtype);
+        if (maps == 2) {
+            ops::DiffAttention da;
+            da.lambda = lambda;
+            da.eps = norm_eps;
+            da.out_scale = 1.f - diff;
+            Mat o = ops::attention_diff(dev, q, kv, ctx, ops::Geometry{n_heads, n_kv_heads, head_dim}, scale, da);
+            return project_out(o, may_defer);
+        }
         ops::AttentionExtras ex;
         ex.sinks = (const float*)sinks.m.p;
         if (has_gate) {
@@ -557,7 +649,13 @@ struct Attention : Mixer {
         }
         ex.wide_weights = true;       // the softmax weights are not to be rounded to eight bits
         Mat o = ops::attention_ex(dev, q, kv, ctx, g, scale, ex);
-        return ops::linear(dev, rt->gemm, o, w_o, out_f32 ? DType::F32 : rt->dtype, may_defer);
+        return project_out(o, may_defer);
+    }
+    // W_o o (+ b_o); with a bias the product is finished here, since the bias joins a finished row
+    MatOrPartials project_out(const Mat& o, bool may_defer) {
+        MatOrPartials y = ops::linear(*rt->dev, rt->gemm, o, w_o, out_f32 ? DType::F32 : rt->dtype, may_defer && !o_bias);
+        if (o_bias) ops::add_bias(*rt->dev, y.m, (const float*)b_o.m.p);
+        return y;
     }
 
     MatOrPartials forward(const Mat& h, const StepContext& ctx, const CacheView& cache, bool writes, bool may_defer) override {
@@ -607,7 +705,8 @@ struct GatedMLP : FeedForward {
             : FeedForward(s, rt), hidden(s.get_int("hidden_size")), inter(s.get_int("intermediate_size")),
               out_f32(s.get_string("output_dtype", "compute") == "float32") {
         act = ops::gate_act_from_name(s.get_string("activation", "silu"));
-        if (act < 0) throw ConfigError("gated_mlp: activation '" + s.get_string("activation", "silu") + "' is not supported (silu, relu, gelu_tanh)");
+        if (act < 0 || act == ops::kActSwishClamped)
+            throw ConfigError("gated_mlp: activation '" + s.get_string("activation", "silu") + "' is not supported (silu, relu, gelu_tanh)");
         if (hidden <= 0 || inter <= 0) throw ConfigError("gated_mlp: sizes must be positive");
         if (s.has("names")) {
             const Json& n = s.params.at("names");
@@ -774,6 +873,20 @@ struct PreNormBlock : Block {
     }
 };
 
+// "prenorm_scaled" is the same layer with a learned factor per channel on each sublayer's output (a layer scale):
+//     x = x + ls1 * mixer(norm1(x));  x = x + ls2 * ffn(norm2(x))
+// the roles "ls1" and "ls2" are parts that give a channel_scale ("layer_scale").  "prenorm_scaled_mixer" is the layer
+// without a feed-forward (roles norm1, ls1).
+struct PreNormScaledBlock : Block {
+    void forward(ResidualStream& stream, const StepContext& ctx, const CacheView& cache, bool writes) override {
+        Mat h = norms.at("norm1")->forward(stream, nullptr, 0);
+        stream.add_normed(mixer->forward(h, ctx, cache, writes, false), norms.at("ls1"));
+        if (!ffn) return;
+        h = norms.at("norm2")->forward(stream, nullptr, 0);
+        stream.add_normed(ffn->forward(h, ctx, false), norms.at("ls2"));
+    }
+};
+
 // "postnorm" is the norm-after-the-sum layer:
 //     x = norm1(a x + mixer(x));  x = norm2(a x + ffn(x))
 // The sublayers read the stream itself, and the normed sum replaces it; the factor a is the norms'
@@ -834,6 +947,9 @@ void register_builtin_parts() {
     reg<EmbeddingPart>()["embedding"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<EmbeddingPart>(new Embedding(s, rt)); };
     reg<HeadPart>()["lm_head"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<HeadPart>(new LMHead(s, rt)); };
     block_reg()["prenorm"] = BlockKind{{"norm1", "norm2"}, [] { return std::unique_ptr<Block>(new PreNormBlock); }};
+    block_reg()["prenorm_scaled"] = BlockKind{{"norm1", "norm2", "ls1", "ls2"}, [] { return std::unique_ptr<Block>(new PreNormScaledBlock); }};
+    block_reg()["prenorm_scaled_mixer"] = BlockKind{{"norm1", "ls1"}, [] { return std::unique_ptr<Block>(new PreNormScaledBlock); }};
+    reg<Norm>()["layer_scale"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<Norm>(new LayerScale(s, rt)); };
 }
 
 }  // namespace

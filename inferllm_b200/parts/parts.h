@@ -178,6 +178,9 @@ public:
     // stream.x += norm(stream.pending), for the norm a sublayer's output passes before it joins the stream
     // (ResidualStream::add_normed); only norms that can stand there override it.
     virtual void add_normed_pending(ResidualStream& stream) { throw EngineError("norm '" + spec.kind + "' cannot norm a sublayer's output into the stream"); }
+    // A part that stands behind a sublayer and is nothing but a factor per channel (a layer scale) gives its float32
+    // factors [size] here, so that the next norm can fold x + factors * pending into its own kernel.
+    virtual const Mat* channel_scale() const { return nullptr; }
 };
 
 inline Mat& ResidualStream::flush() {

@@ -17,6 +17,12 @@
 // chosen; the weights are the chosen experts' s, as they are unless `renormalize`.  `shared` {intermediate_size,
 // activation, names} adds a gated feed-forward that every token goes through (a "gated_mlp" part below the prefix
 // `shared_prefix`), its float32 output summed with the experts' in the kernel that combines them.
+//
+// A third way, `scoring` = "sigmoid": s_e = sigmoid(z_e), every expert by itself; choice, groups and weights as for
+// softmax_all.  Three more parameters of the scored ways: `group_score_top` n (a group's score is the sum of its n largest
+// choice scores; 1 if not given), `weight_scale` (the weights are multiplied by it at the end) and `sum_eps` (added to the
+// sum the weights are divided by).  And one more activation of the experts, "swish_clamped" with `activation_limit` L:
+// g = min(W_gate h, L), u = clamp(W_up h, -L, L), y = g sigmoid(1.702 g) (u + 1).
 #include "parts/parts.h"
 
 namespace illm {
@@ -27,8 +33,9 @@ struct RoutedMLP : FeedForward {
     long long hidden, inter;
     int experts, top, act;
     bool has_bias;
-    bool score_all, has_correction, renorm;
-    int groups = 1, keep = 1;
+    bool score_all, score_sigmoid, has_correction, renorm;
+    int groups = 1, keep = 1, group_top = 1;
+    float weight_scale = 1.f, sum_eps = 0.f, act_limit = 0.f;
     std::unique_ptr<FeedForward> shared;
     std::string shared_prefix;
     OwnedMat correction;
@@ -40,12 +47,24 @@ struct RoutedMLP : FeedForward {
     RoutedMLP(const PartSpec& s, Runtime* rt)
             : FeedForward(s, rt), hidden(s.get_int("hidden_size")), inter(s.get_int("intermediate_size")), experts((int)s.get_int("experts")),
               top((int)s.get_int("top")), act(ops::gate_act_from_name(s.get_string("activation", "silu"))), has_bias(s.get_bool("router_bias", false)),
-              score_all(s.get_string("scoring", "softmax_chosen") == "softmax_all"), has_correction(s.get_bool("choice_correction", false)),
+              score_all(s.get_string("scoring", "softmax_chosen") == "softmax_all"), score_sigmoid(s.get_string("scoring", "softmax_chosen") == "sigmoid"),
+              has_correction(s.get_bool("choice_correction", false)),
               renorm(s.get_bool("renormalize", false)), shared_prefix(s.get_string("shared_prefix", "shared.")) {
         const std::string sc = s.get_string("scoring", "softmax_chosen");
-        if (sc != "softmax_chosen" && sc != "softmax_all") throw ConfigError("routed_mlp: scoring '" + sc + "' is not supported (softmax_chosen, softmax_all)");
-        if (!score_all && (has_correction || s.has("groups"))) throw ConfigError("routed_mlp: a choice correction and groups need scoring = softmax_all");
-        if (score_all && has_bias) throw ConfigError("routed_mlp: scoring = softmax_all takes a choice correction, not a router bias");
+        if (sc != "softmax_chosen" && sc != "softmax_all" && sc != "sigmoid")
+            throw ConfigError("routed_mlp: scoring '" + sc + "' is not supported (softmax_chosen, softmax_all, sigmoid)");
+        const bool scored = score_all || score_sigmoid;
+        if (!scored && (has_correction || s.has("groups") || s.has("group_score_top") || s.has("weight_scale") || s.has("sum_eps")))
+            throw ConfigError("routed_mlp: a choice correction, groups, weight_scale and sum_eps need scoring = softmax_all or sigmoid");
+        if (scored && has_bias) throw ConfigError("routed_mlp: scoring = " + sc + " takes a choice correction, not a router bias");
+        group_top = (int)s.get_int("group_score_top", 1);
+        weight_scale = (float)s.get_double("weight_scale", 1.0);
+        sum_eps = (float)s.get_double("sum_eps", 0.0);
+        if (group_top < 1 || group_top > 4) throw ConfigError("routed_mlp: group_score_top must be 1 to 4");
+        if (act == ops::kActSwishClamped) {
+            act_limit = (float)s.get_double("activation_limit");
+            if (!(act_limit > 0.f)) throw ConfigError("routed_mlp: activation_limit must be positive");
+        }
         if (s.has("groups")) {
             const Json& g = s.params.at("groups");
             if (!g.is_object() || !g.has("count") || !g.has("keep") || !g.at("count").is_int() || !g.at("keep").is_int())
@@ -64,7 +83,7 @@ struct RoutedMLP : FeedForward {
         }
         if (hidden <= 0 || inter <= 0 || experts <= 0 || top <= 0 || top > experts)
             throw ConfigError("routed_mlp: sizes must be positive and top at most the number of experts");
-        if (act < 0) throw ConfigError("routed_mlp: activation '" + s.get_string("activation", "silu") + "' is not supported (silu, relu, gelu_tanh)");
+        if (act < 0) throw ConfigError("routed_mlp: activation '" + s.get_string("activation", "silu") + "' is not supported (silu, relu, gelu_tanh, swish_clamped)");
         names = {{"router", "router.weight"}, {"router_bias", "router.bias"}, {"correction", "correction"}, {"expert", "experts."}, {"gate", "gate_proj.weight"},
                  {"up", "up_proj.weight"}, {"down", "down_proj.weight"}};
         if (s.has("names"))
@@ -116,10 +135,14 @@ struct RoutedMLP : FeedForward {
         Device& dev = *rt->dev;
         Mat logits = ops::linear(dev, rt->gemm, h, w_router.m, DType::F32, false).m;
         ops::MoeRouting route;
-        route.scoring = score_all ? 1 : 0;
+        route.scoring = score_all ? 1 : score_sigmoid ? 2 : 0;
         route.groups = groups;
         route.keep = keep;
-        route.renorm = score_all ? renorm : true;
+        route.group_top = group_top;
+        route.weight_scale = weight_scale;
+        route.sum_eps = sum_eps;
+        route.act_limit = act_limit;
+        route.renorm = (score_all || score_sigmoid) ? renorm : true;
         route.bias = has_bias ? (const float*)b_router.m.p : has_correction ? (const float*)correction.m.p : nullptr;
         Mat plus;
         if (shared) {
