@@ -216,6 +216,31 @@ def kudonex_config(z, vocab=32000, max_positions=4096):
                 vocab=vocab, width=z["width"], max_positions=max_positions, canon=dict(taps=3), embedding=dict(scale=1.0))
 
 
+TUKULORN_LAYERS = (("attention", "dense"), ("latent_attention", "moe"), ("attention", "moe"), ("latent_attention", "dense"),
+                   ("attention", "dense"), ("latent_attention", "moe"))
+
+
+def tukulorn_config(z, vocab=32000, max_positions=4096):
+    """Six layers of the Tukulorn design at the size z: differential attention with the size's head counts, two score
+    maps of half the head size and values of the whole head size (the same query, key and value widths as a plain
+    attention layer of the size), a query temperature every 128 positions; latent attention with a latent of 96
+    channels beside 32 rotated ones (a cache row of 128 channels, as Vizosun's latent) and a window of 1,024; dense
+    feed-forwards of the size's width, routed ones with 8 experts in 4 groups (2 kept) of half that width of which a
+    token uses 2 (the same active matrix elements); layers 1 and 2 run twice (so eight layer runs, as Vizosun)."""
+    layers = []
+    for t, kind in TUKULORN_LAYERS:
+        if t == "attention":
+            m = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["d"] // 2, vdim=z["d"], diff=0.5, scale=(z["d"] // 2) ** -0.5, q_temp=dict(coef=0.3, every=128))
+        else:
+            m = dict(heads=z["heads"], dim=z["d"], rot_dim=32, vdim=z["d"], kv_rank=96, scale=(z["d"] + 32) ** -0.5, mask=dict(size=1024),
+                     rot=dict(base=10000.0, dims=32))
+        mlp = dict(kind="dense", ff=z["ff"]) if kind == "dense" else \
+            dict(kind="moe", expert=dict(ff=z["ff"] // 2, limit=7.0), router=dict(experts=8, top=2, scale=1.0, groups=dict(count=4, keep=2)))
+        layers.append(dict(type=t, mixer=m, mlp=mlp))
+    return dict(architecture="Tukulorn", layers=layers, norm=dict(eps=1e-6), vocab=vocab, width=z["width"], max_positions=max_positions,
+                loop=dict(start=1, stop=3, times=2))
+
+
 def llama_twin(z, vocab=32000, max_positions=4096):
     return dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=len(DESIGN_LAYERS),
                 num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["d"], intermediate_size=z["ff"],
@@ -226,7 +251,7 @@ def llama_twin(z, vocab=32000, max_positions=4096):
 def run_design(args):
     """Prompt and decode throughput of a design at a few layer sizes, each beside the closest other
     model of the same width, feed-forward, head counts and number of layers (Vokelix beside LLaMA;
-    Vizosun beside Vokelix and LLaMA; Kudonex beside all three), through Engine.step; and
+    Vizosun beside Vokelix and LLaMA; Kudonex and Tukulorn beside all three), through Engine.step; and
     where each of the two spends its time, kernel by kernel (the driver's activity records of one step).
     One JSON line per (size, model)."""
     import torch
@@ -267,6 +292,8 @@ def run_design(args):
             arms = (("vizosun", vizosun_config(z)),) + arms
         if args.design == "kudonex":
             arms = (("kudonex", kudonex_config(z)), ("vizosun", vizosun_config(z))) + arms
+        if args.design == "tukulorn":
+            arms = (("tukulorn", tukulorn_config(z)), ("vizosun", vizosun_config(z))) + arms
         for which, cfgd in arms:
             eng = Engine.from_config(config_from_dict(cfgd), EngineOptions(dtype="bfloat16", max_tokens=max(B * (C + 64), NP * (T + 64)) + 64,
                                                                            max_seq_len=4096, max_batch=max(B, NP, 8)), seed=0)
@@ -296,7 +323,7 @@ def run_design(args):
             dec_ms = timed(one, K)
             for s in slots:
                 eng.end_sequence(s)
-            print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else ["/".join(x) for x in VIZOSUN_LAYERS] if which == "vizosun" else list(KUDONEX_LAYERS) if which == "kudonex" else len(DESIGN_LAYERS),
+            print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else ["/".join(x) for x in VIZOSUN_LAYERS] if which == "vizosun" else list(KUDONEX_LAYERS) if which == "kudonex" else ["/".join(x) for x in TUKULORN_LAYERS] if which == "tukulorn" else len(DESIGN_LAYERS),
                               "prefill_tokens": T, "prefill_prompts": NP, "prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(NP * T / pf_ms * 1e3, 1),
                               "decode_batch": B, "decode_context": C, "decode_ms": round(dec_ms, 4),
                               "decode_tok_s": round(B / dec_ms * 1e3, 1), "prefill_kernels_us": pf_kernels,
@@ -529,7 +556,7 @@ def main():
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
                     "each (or 'toN': until position N), through the Python entry point; 'config' = the workload of --model "
                     "(8b: 16:64:2048:256, 13b: 32:128:1024:to4096)")
-    ap.add_argument("--design", choices=["vokelix", "vizosun", "kudonex"], help="beside the default workload: prompt and decode throughput of this design "
+    ap.add_argument("--design", choices=["vokelix", "vizosun", "kudonex", "tukulorn"], help="beside the default workload: prompt and decode throughput of this design "
                     "at a few layer sizes, each next to LLaMA layers of equal size, with the time per kernel")
     ap.add_argument("--design-size", default="1k,2k,4k", help="with --design: sizes to run (1k, 2k, 4k: the width)")
     ap.add_argument("--design-tokens", type=int, default=2048, help="with --design: tokens of the prompt")

@@ -148,7 +148,12 @@ int illm_moe_route_ex2(const float* logits, const float* bias, int T, int E, int
 int illm_moe_gemm_ex(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated, int act, float act_limit, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows, void* stream);
 int illm_moe_gemm_tc_ex(const void* xs, const void* w, void* y, int P, int E, int N, int K, int gated, int act, float act_limit, int tiles, const int* tile_expert, const int* tile_row0, const int* tile_rows, int* err, void* stream);
 // attention_diff.cu
-int illm_attention_diff(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int dv, int page_size, int window, float scale, float lambda, float eps, float out_scale, void* stream);
+int illm_attention_diff(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int dv, int page_size, int window, float scale, float lambda, float eps, float out_scale, int splits, float* scratch, void* stream);
+long long illm_attention_diff_scratch(int T, int nh, int dv, int splits);
+int illm_attention_diff_mma_supported(int d, int dv);
+int illm_attention_diff_decode_supported(int nh, int nkv, int d, int dv);
+int illm_attention_diff_decode(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int T, int nh, int nkv, int d, int dv, int page_size, int window, float scale, float lambda, float eps, float out_scale, long long max_len, int splits, float* scratch, void* stream);
+int illm_attention_diff_mma(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int dv, int page_size, int window, float scale, float lambda, float eps, float out_scale, void* stream);
 // latent_attention.cu
 int illm_latent_attention_any_gated(const void* q, const void* kc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int H, int R, int page_size, int window, float scale, const float* gate, int gate_stride, void* stream);
 int illm_latent_rope_prep(const float* x, int ld, int q_off, int H, int d, int dr, int c_off, int R, const float* wkv, float eps, const float* cos_sin, int rot, int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* q_nope, int q_f32, void* qa, void* kc, int act_dtype, int T, int* err, void* stream);

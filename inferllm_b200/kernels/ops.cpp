@@ -750,11 +750,36 @@ Mat attention_diff(Device& dev, const Mat& q, const KVView& kv, const StepView& 
     if (!kv.k || !kv.v || kv.dtype != q.dtype || kv.n_kv_heads != g.n_kv_heads || kv.head_dim != 2 * g.head_dim || q.cols < (long long)g.n_heads * 2 * g.head_dim)
         throw KernelError("attention_diff: the cache entry must hold key rows of two maps (2 x " + std::to_string(g.head_dim) + " channels) in the queries' dtype");
     Mat out = new_mat(dev, q.rows, (long long)g.n_heads * dv, q.dtype);
+    if (q.dtype == DType::BF16 && !ctx.is_decode && illm_attention_diff_mma_supported(g.head_dim, dv) && q.cols % 8 == 0) {
+        check_kernel(illm_attention_diff_mma(q.p, (int)q.cols, kv.k, kv.v, kv.block_table, kv.width, ctx.cu_q, ctx.seq_lens, out.p, ctx.B, ctx.max_q, g.n_heads,
+                                             g.n_kv_heads, g.head_dim, dv, kv.page_size, kv.window, scale, p.lambda, p.eps, p.out_scale, dev.stream()),
+                     "attention_diff_mma");
+        return out;
+    }
+    // grids and scratch of a single-token step are sized for the longest sequence the cache allows, so that the launch is
+    // the same at every step
+    if (q.dtype == DType::BF16 && ctx.is_decode && illm_attention_diff_decode_supported(g.n_heads, g.n_kv_heads, g.head_dim, dv)) {
+        const int group = g.n_heads / g.n_kv_heads, hb = group >= 8 ? 8 : group > 2 ? 4 : group;
+        const int splits = attention_diff_splits(q.rows, g.n_kv_heads * (int)ceil_div(group, hb), ctx.max_seq_len, dev.n_sms());
+        float* scratch = dev.alloc_n<float>((size_t)illm_attention_diff_scratch((int)q.rows, g.n_heads, dv, splits));
+        check_kernel(illm_attention_diff_decode(q.p, (int)q.cols, kv.k, kv.v, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, (int)q.rows, g.n_heads,
+                                                g.n_kv_heads, g.head_dim, dv, kv.page_size, kv.window, scale, p.lambda, p.eps, p.out_scale, ctx.max_seq_len,
+                                                splits, scratch, dev.stream()),
+                     "attention_diff_decode");
+        return out;
+    }
     check_kernel(illm_attention_diff(q.p, (int)q.cols, kv.k, kv.v, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, code_of(q.dtype, "attention_diff"),
                                      (int)q.rows, g.n_heads, g.n_kv_heads, g.head_dim, dv, kv.page_size, kv.window, scale, p.lambda, p.eps, p.out_scale,
-                                     dev.stream()),
+                                     1, nullptr, dev.stream()),
                  "attention_diff");
     return out;
+}
+
+int attention_diff_splits(long long T, int head_groups, long long max_seq_len, int n_sms) {
+    const long long pairs = std::max<long long>(1, T * head_groups);
+    long long s = ceil_div(8LL * n_sms, pairs);
+    s = std::min<long long>(s, std::max<long long>(1, ceil_div(max_seq_len, 256)));
+    return (int)std::max<long long>(1, std::min<long long>(s, 64));
 }
 
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale) {

@@ -204,9 +204,16 @@ Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView&
 // (a head's row is [q_1, q_2]), the cache entry's key rows [k_1, k_2] (kv.head_dim == 2 d) and value rows of
 // kv.v_head_dim; o = a_1 - lambda a_2, divided by its root mean square over the head's values (eps inside the root), times
 // out_scale.  g.head_dim is d, the size of ONE map.  Returns [T, heads * v_head_dim] in q's dtype.
+// Kernels: prompts in bfloat16 with d and dv multiples of 16 (d up to 192, dv up to 128) on warp-level MMA; bfloat16
+// steps of one token per sequence (d a multiple of 8, dv even) on a kernel that reads every key and value row once for
+// the query heads that share it, the keys dealt to attention_diff_splits blocks; everything else (the float32 mode, whose
+// sums keep one order) on the plain kernel.
 struct DiffAttention {
     float lambda = 0.f, eps = 1e-6f, out_scale = 1.f;
 };
+// Blocks per (token, group of query heads) of a single-token step: enough to give every SM about eight blocks (half of them idle when the sequences are half as long as the cache allows), at most
+// one per 256 keys of the longest sequence the cache allows, at most 64.
+int attention_diff_splits(long long T, int head_groups, long long max_seq_len, int n_sms);
 Mat attention_diff(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const DiffAttention& p);
 // Attention of the step's tokens over a cache entry: picks the kernel for the dtype, head size and kind of step.
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
