@@ -230,13 +230,13 @@ extern "C" int illm_attention_diff(const void* q, int q_stride, const void* kc, 
 // head, a share of the keys) and works through its share in rounds of 256 keys: (1) a thread per key reads the key row
 // once, 16 bytes at a time, for the scores of all its heads and both maps (float32), and notes where the key's value
 // row lies; (2) a warp per (head, map) takes the round's maximum, moves the running maximum and sum, and turns the
-// scores into weights; (3) a thread per pair of value channels and slice of the keys adds the weighted value rows for
-// all heads and maps, every row read once, the loads independent of one another.  The slices are added in a fixed
+// scores into weights; (3) a thread per VEC value channels (16 or 8 bytes) and slice of the keys adds the weighted value
+// rows for all heads and maps, every row read once, the loads independent of one another.  The slices are added in a fixed
 // order and the block's share goes to attention_diff_merge_kernel.  Blocks whose share holds no visible key leave an
 // empty share.  The grid depends on the longest sequence the cache allows, not on the step.
 #define DD_THREADS 256
 
-template <int HB>
+template <int HB, int VEC>
 __global__ void __launch_bounds__(DD_THREADS)
 attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ token_pos,
@@ -248,10 +248,10 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf1
     const int t = blockIdx.x, hk = blockIdx.y / subs, sub = blockIdx.y - hk * subs, z = blockIdx.z, splits = gridDim.z;
     const int g0 = sub * HB, nhb = (group - g0 < HB) ? group - g0 : HB;
     const int h0 = hk * group + g0;
-    const int tv = dv / 2, KS = DD_THREADS / tv;          // threads per value row, slices of the keys
+    const int tv = dv / VEC, KS = DD_THREADS / tv;        // threads per value row, slices of the keys
     long long* rowoff = reinterpret_cast<long long*>(dd_raw);                 // [256] row of the key in the pages
     float* qs = reinterpret_cast<float*>(rowoff + DD_THREADS);                // [HB][2 d]
-    float* S = qs + HB * 2 * d;                                               // [HB * 2][256] scores, then weights
+    float* S = qs + HB * 2 * d;                                               // [256][HB * 2] scores, then weights (a key's rows side by side)
     float* red = S + HB * 2 * DD_THREADS;                                     // [KS][HB * 2][dv]
     __shared__ float run_m[HB * 2], run_l[HB * 2], fac[HB * 2];
 
@@ -262,6 +262,18 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf1
     if (k_begin < lo) k_begin = lo;
     if (k_end > p + 1) k_end = p + 1;
     const int* bt = block_table + (size_t)token_seq[t] * max_pages;
+    if (k_begin >= k_end) {          // no visible key in this block's share: an empty share, at once
+        for (int i = tid; i < nhb * 2 * dv; i += DD_THREADS) {
+            const int row = i / dv, c = i - row * dv;
+            float* dst = part + ((((size_t)t * nh + h0 + (row >> 1)) * splits + z) * 2 + (row & 1)) * (dv + 2);
+            dst[2 + c] = 0.f;
+            if (c == 0) {
+                dst[0] = -INFINITY;
+                dst[1] = 0.f;
+            }
+        }
+        return;
+    }
 
     for (int i = tid; i < nhb * 2 * d; i += DD_THREADS) qs[i] = to_f32(q[(size_t)t * q_stride + (size_t)h0 * 2 * d + i]);
     if (tid < HB * 2) {
@@ -269,9 +281,11 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf1
         run_l[tid] = 0.f;
     }
     const int cpair = tid % tv, ks = tid / tv;
-    float acc[HB][2][2];
+    float acc[HB][2][VEC];
 #pragma unroll
-    for (int g = 0; g < HB; g++) acc[g][0][0] = acc[g][0][1] = acc[g][1][0] = acc[g][1][1] = 0.f;
+    for (int g = 0; g < HB; g++)
+#pragma unroll
+        for (int i = 0; i < VEC; i++) acc[g][0][i] = acc[g][1][i] = 0.f;
     __syncthreads();
 
     for (int r0 = k_begin; r0 < k_end; r0 += DD_THREADS) {
@@ -288,7 +302,7 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf1
                 const long long row = ((long long)page * nkv + hk) * page_size + (key % page_size);
                 rowoff[tid] = row;
                 const bf16* kr = kc + row * 2 * d;
-#pragma unroll 4
+#pragma unroll 8
                 for (int c = 0; c < d; c += 8) {
                     float f1[8], f2[8];
                     load8(kr + c, f1);
@@ -296,34 +310,39 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf1
 #pragma unroll
                     for (int g = 0; g < HB; g++) {
                         if (g < nhb) {
-                            const float* qg = qs + g * 2 * d;
-#pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                dot[g][0] = fmaf(qg[c + i], f1[i], dot[g][0]);
-                                dot[g][1] = fmaf(qg[d + c + i], f2[i], dot[g][1]);
-                            }
+                            const float4* qa = reinterpret_cast<const float4*>(qs + g * 2 * d + c);        // d % 8 == 0: 16-byte reads, the same for all lanes
+                            const float4* qb = reinterpret_cast<const float4*>(qs + g * 2 * d + d + c);
+                            const float4 a0 = qa[0], a1 = qa[1], b0 = qb[0], b1 = qb[1];
+                            dot[g][0] = fmaf(a0.x, f1[0], dot[g][0]); dot[g][0] = fmaf(a0.y, f1[1], dot[g][0]);
+                            dot[g][0] = fmaf(a0.z, f1[2], dot[g][0]); dot[g][0] = fmaf(a0.w, f1[3], dot[g][0]);
+                            dot[g][0] = fmaf(a1.x, f1[4], dot[g][0]); dot[g][0] = fmaf(a1.y, f1[5], dot[g][0]);
+                            dot[g][0] = fmaf(a1.z, f1[6], dot[g][0]); dot[g][0] = fmaf(a1.w, f1[7], dot[g][0]);
+                            dot[g][1] = fmaf(b0.x, f2[0], dot[g][1]); dot[g][1] = fmaf(b0.y, f2[1], dot[g][1]);
+                            dot[g][1] = fmaf(b0.z, f2[2], dot[g][1]); dot[g][1] = fmaf(b0.w, f2[3], dot[g][1]);
+                            dot[g][1] = fmaf(b1.x, f2[4], dot[g][1]); dot[g][1] = fmaf(b1.y, f2[5], dot[g][1]);
+                            dot[g][1] = fmaf(b1.z, f2[6], dot[g][1]); dot[g][1] = fmaf(b1.w, f2[7], dot[g][1]);
                         }
                     }
                 }
             }
 #pragma unroll
             for (int g = 0; g < HB; g++) {
-                S[(g * 2) * DD_THREADS + tid] = valid ? dot[g][0] * scale : -INFINITY;
-                S[(g * 2 + 1) * DD_THREADS + tid] = valid ? dot[g][1] * scale : -INFINITY;
+                S[tid * (HB * 2) + g * 2] = valid ? dot[g][0] * scale : -INFINITY;
+                S[tid * (HB * 2) + g * 2 + 1] = valid ? dot[g][1] * scale : -INFINITY;
             }
         }
         __syncthreads();
         // (2) the round's maximum, the running maximum and sum, the weights
         for (int row = warp; row < nhb * 2; row += DD_THREADS / 32) {
-            float* sr = S + row * DD_THREADS;
+            float* sr = S + row;
             float mx = -INFINITY;
-            for (int k = lane; k < DD_THREADS; k += 32) mx = fmaxf(mx, sr[k]);
+            for (int k = lane; k < DD_THREADS; k += 32) mx = fmaxf(mx, sr[k * (HB * 2)]);
             mx = warp_max(mx);
             const float m_old = run_m[row], m_new = fmaxf(m_old, mx);
             float sum = 0.f;
             for (int k = lane; k < DD_THREADS; k += 32) {
-                const float w = (k < nkeys) ? expf(sr[k] - m_new) : 0.f;
-                sr[k] = w;
+                const float w = (k < nkeys) ? expf(sr[k * (HB * 2)] - m_new) : 0.f;
+                sr[k * (HB * 2)] = w;
                 sum += w;
             }
             sum = warp_sum(sum);
@@ -335,29 +354,63 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf1
             }
         }
         __syncthreads();
-        // (3) weighted value rows: this thread's two channels, every KS-th key
+        // (3) weighted value rows: this thread's VEC channels, every KS-th key
         if (ks < KS) {
 #pragma unroll
             for (int g = 0; g < HB; g++) {
                 if (g < nhb) {
                     const float f0 = fac[g * 2], f1 = fac[g * 2 + 1];
-                    acc[g][0][0] *= f0;
-                    acc[g][0][1] *= f0;
-                    acc[g][1][0] *= f1;
-                    acc[g][1][1] *= f1;
+#pragma unroll
+                    for (int i = 0; i < VEC; i++) {
+                        acc[g][0][i] *= f0;
+                        acc[g][1][i] *= f1;
+                    }
                 }
             }
-#pragma unroll 8
-            for (int k = ks; k < nkeys; k += KS) {
-                const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vc + rowoff[k] * dv + 2 * cpair));
+            // eight value rows at a time: all their loads are issued before the first is used, so that a block keeps tens of
+            // kilobytes on their way (few warps run on an SM in a step of few tokens, and nothing else hides the latency)
+            constexpr int KU = 8;
+            for (int kb = ks; kb < nkeys; kb += KS * KU) {
+                unsigned raw[KU][VEC / 2];
 #pragma unroll
-                for (int g = 0; g < HB; g++) {
-                    if (g < nhb) {
-                        const float w0 = S[(g * 2) * DD_THREADS + k], w1 = S[(g * 2 + 1) * DD_THREADS + k];
-                        acc[g][0][0] = fmaf(w0, v.x, acc[g][0][0]);
-                        acc[g][0][1] = fmaf(w0, v.y, acc[g][0][1]);
-                        acc[g][1][0] = fmaf(w1, v.x, acc[g][1][0]);
-                        acc[g][1][1] = fmaf(w1, v.y, acc[g][1][1]);
+                for (int j = 0; j < KU; j++) {
+                    const int k = kb + j * KS;
+                    if (k < nkeys) {
+                        const bf16* vr = vc + rowoff[k] * dv + VEC * cpair;
+                        if (VEC == 8) {
+                            const uint4 u = *reinterpret_cast<const uint4*>(vr);
+                            raw[j][0] = u.x; raw[j][1] = u.y; raw[j][VEC / 2 - 2] = u.z; raw[j][VEC / 2 - 1] = u.w;
+                        } else {
+                            const uint2 u = *reinterpret_cast<const uint2*>(vr);
+                            raw[j][0] = u.x; raw[j][1] = u.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < VEC / 2; i++) raw[j][i] = 0u;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < KU; j++) {
+                    const int k = kb + j * KS;
+                    if (k >= nkeys) break;
+                    float v[VEC];
+#pragma unroll
+                    for (int i = 0; i < VEC / 2; i++) {
+                        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[j][i]));
+                        v[2 * i] = f.x;
+                        v[2 * i + 1] = f.y;
+                    }
+#pragma unroll
+                    for (int g = 0; g < HB; g++) {
+                        if (g < nhb) {
+                            const float2 w01 = *reinterpret_cast<const float2*>(S + k * (HB * 2) + g * 2);
+                            const float w0 = w01.x, w1 = w01.y;
+#pragma unroll
+                            for (int i = 0; i < VEC; i++) {
+                                acc[g][0][i] = fmaf(w0, v[i], acc[g][0][i]);
+                                acc[g][1][i] = fmaf(w1, v[i], acc[g][1][i]);
+                            }
+                        }
                     }
                 }
             }
@@ -370,10 +423,9 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf1
         for (int g = 0; g < HB; g++) {
             if (g < nhb) {
 #pragma unroll
-                for (int mp = 0; mp < 2; mp++) {
-                    red[((size_t)ks * HB * 2 + g * 2 + mp) * dv + 2 * cpair] = acc[g][mp][0];
-                    red[((size_t)ks * HB * 2 + g * 2 + mp) * dv + 2 * cpair + 1] = acc[g][mp][1];
-                }
+                for (int mp = 0; mp < 2; mp++)
+#pragma unroll
+                    for (int i = 0; i < VEC; i++) red[((size_t)ks * HB * 2 + g * 2 + mp) * dv + VEC * cpair + i] = acc[g][mp][i];
             }
         }
     }
@@ -397,7 +449,7 @@ extern "C" int illm_attention_diff_decode_keys(long long max_len, int splits) {
     return (int)((per + DD_THREADS - 1) / DD_THREADS * DD_THREADS);
 }
 extern "C" int illm_attention_diff_decode_supported(int nh, int nkv, int d, int dv) {
-    return nkv > 0 && nh % nkv == 0 && d > 0 && d <= AD_MAX_D && d % 8 == 0 && dv >= 2 && dv <= AD_MAX_D && dv % 2 == 0;
+    return nkv > 0 && nh % nkv == 0 && d > 0 && d <= AD_MAX_D && d % 8 == 0 && dv >= 8 && dv <= AD_MAX_D && dv % 8 == 0 && dv / 4 <= DD_THREADS;
 }
 
 // q [T, q_stride] bfloat16, one token per sequence; scratch: illm_attention_diff_scratch(T, nh, dv, splits) floats (also for
@@ -414,20 +466,21 @@ extern "C" int illm_attention_diff_decode(const void* q, int q_stride, const voi
     const int subs = (group + hb - 1) / hb;
     if ((long long)nkv * subs > 65535) return ILLM_ERR_BAD_ARG;
     const int keys = illm_attention_diff_decode_keys(max_len, splits);
-    const int ksl = DD_THREADS / (dv / 2);
+    const int vec = hb == 8 ? 4 : 8;          // channels per thread: sixteen heads-and-maps times eight channels would not fit the registers
+    const int ksl = DD_THREADS / (dv / vec);
     const size_t smem = (size_t)DD_THREADS * sizeof(long long) + ((size_t)hb * 2 * d + (size_t)hb * 2 * DD_THREADS + (size_t)ksl * hb * 2 * dv) * sizeof(float);
     dim3 grid(T, nkv * subs, splits);
-#define ILLM_DD(HB)                                                                                                                        \
+#define ILLM_DD(HB, VEC)                                                                                                                   \
     do {                                                                                                                                   \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_diff_decode_kernel<HB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        illm_launch(attention_diff_decode_kernel<HB>, grid, dim3(DD_THREADS), smem, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_diff_decode_kernel<HB, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        illm_launch(attention_diff_decode_kernel<HB, VEC>, grid, dim3(DD_THREADS), smem, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, \
                     block_table, max_pages, token_pos, token_seq, scratch, nh, nkv, d, dv, page_size, window, scale, keys);                \
     } while (0)
     if (smem > 200 * 1024) return ILLM_ERR_BAD_ARG;
-    if (hb == 8) ILLM_DD(8);
-    else if (hb == 4) ILLM_DD(4);
-    else if (hb == 2) ILLM_DD(2);
-    else ILLM_DD(1);
+    if (hb == 8) ILLM_DD(8, 4);
+    else if (hb == 4) ILLM_DD(4, 8);
+    else if (hb == 2) ILLM_DD(2, 8);
+    else ILLM_DD(1, 8);
 #undef ILLM_DD
     illm_launch(attention_diff_merge_kernel<bf16>, dim3(T, nh), dim3(AD_MAX_D), 0, s, (const float*)scratch, (bf16*)out, nh, dv, splits, lambda, eps, out_scale);
     return illm_launch_status();

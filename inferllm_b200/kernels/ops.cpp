@@ -777,7 +777,7 @@ Mat attention_diff(Device& dev, const Mat& q, const KVView& kv, const StepView& 
 
 int attention_diff_splits(long long T, int head_groups, long long max_seq_len, int n_sms) {
     const long long pairs = std::max<long long>(1, T * head_groups);
-    long long s = ceil_div(8LL * n_sms, pairs);
+    long long s = std::max<long long>(1, 2LL * n_sms / pairs);
     s = std::min<long long>(s, std::max<long long>(1, ceil_div(max_seq_len, 256)));
     return (int)std::max<long long>(1, std::min<long long>(s, 64));
 }

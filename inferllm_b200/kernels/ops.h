@@ -211,7 +211,7 @@ Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView&
 struct DiffAttention {
     float lambda = 0.f, eps = 1e-6f, out_scale = 1.f;
 };
-// Blocks per (token, group of query heads) of a single-token step: enough to give every SM about eight blocks (half of them idle when the sequences are half as long as the cache allows), at most
+// Blocks per (token, group of query heads) of a single-token step: as many as fit the GPU at once (two blocks of many heads, or more of few, per SM; a block keeps tens of kilobytes of loads in flight), at most
 // one per 256 keys of the longest sequence the cache allows, at most 64.
 int attention_diff_splits(long long T, int head_groups, long long max_seq_len, int n_sms);
 Mat attention_diff(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const DiffAttention& p);
