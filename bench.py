@@ -223,17 +223,17 @@ TUKULORN_LAYERS = (("attention", "dense"), ("latent_attention", "moe"), ("attent
 def tukulorn_config(z, vocab=32000, max_positions=4096):
     """Six layers of the Tukulorn design at the size z: differential attention with the size's head counts, two score
     maps of half the head size and values of the whole head size (the same query, key and value widths as a plain
-    attention layer of the size), a query temperature every 128 positions; latent attention with a latent of 96
-    channels beside 32 rotated ones (a cache row of 128 channels, as Vizosun's latent) and a window of 1,024; dense
+    attention layer of the size), a query temperature every 256 positions; latent attention with a latent of 64
+    channels beside 64 rotated ones (a cache row of 128 channels, as Vizosun's latent) and a window of 1,024; dense
     feed-forwards of the size's width, routed ones with 8 experts in 4 groups (2 kept) of half that width of which a
     token uses 2 (the same active matrix elements); layers 1 and 2 run twice (so eight layer runs, as Vizosun)."""
     layers = []
     for t, kind in TUKULORN_LAYERS:
         if t == "attention":
-            m = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["d"] // 2, vdim=z["d"], diff=0.5, scale=(z["d"] // 2) ** -0.5, q_temp=dict(coef=0.3, every=128))
+            m = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["d"] // 2, vdim=z["d"], diff=0.4, scale=(z["d"] // 2) ** -0.5, q_temp=dict(coef=0.25, every=256))
         else:
-            m = dict(heads=z["heads"], dim=z["d"], rot_dim=32, vdim=z["d"], kv_rank=96, scale=(z["d"] + 32) ** -0.5, mask=dict(size=1024),
-                     rot=dict(base=10000.0, dims=32))
+            m = dict(heads=z["heads"], dim=z["d"], rot_dim=64, vdim=z["d"], kv_rank=64, scale=(z["d"] + 64) ** -0.5, mask=dict(size=1024),
+                     rot=dict(base=500000.0, dims=64))
         mlp = dict(kind="dense", ff=z["ff"]) if kind == "dense" else \
             dict(kind="moe", expert=dict(ff=z["ff"] // 2, limit=7.0), router=dict(experts=8, top=2, scale=1.0, groups=dict(count=4, keep=2)))
         layers.append(dict(type=t, mixer=m, mlp=mlp))
