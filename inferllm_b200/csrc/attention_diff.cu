@@ -680,16 +680,19 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* 
                     o[mp][i][2] *= corr[1];
                     o[mp][i][3] *= corr[1];
                 }
+                // the two terms of the weights in two passes over the staged values: an accumulator's two MMAs of a key
+                // step then lie a whole pass apart instead of back to back (the second waits for the first's result)
 #pragma unroll
                 for (int ks = 0; ks < DM_BN / 16; ks++) {
 #pragma unroll
-                    for (int np = 0; np < NT_V / 2; np++) {
-                        unsigned b0, b1, b2, b3;
-                        dm_ldsm4_trans(b0, b1, b2, b3, dm_smem(vb + (ks * 16 + (mtx & 1) * 8 + (lane & 7)) * LDV + (np * 2 + (mtx >> 1)) * 8));
-                        dm_mma(o[mp][np * 2], ph[ks], b0, b1);
-                        dm_mma(o[mp][np * 2], pl[ks], b0, b1);
-                        dm_mma(o[mp][np * 2 + 1], ph[ks], b2, b3);
-                        dm_mma(o[mp][np * 2 + 1], pl[ks], b2, b3);
+                    for (int term = 0; term < 2; term++) {
+#pragma unroll
+                        for (int np = 0; np < NT_V / 2; np++) {
+                            unsigned b0, b1, b2, b3;
+                            dm_ldsm4_trans(b0, b1, b2, b3, dm_smem(vb + (ks * 16 + (mtx & 1) * 8 + (lane & 7)) * LDV + (np * 2 + (mtx >> 1)) * 8));
+                            dm_mma(o[mp][np * 2], term ? pl[ks] : ph[ks], b0, b1);
+                            dm_mma(o[mp][np * 2 + 1], term ? pl[ks] : ph[ks], b2, b3);
+                        }
                     }
                 }
             }
