@@ -148,6 +148,9 @@ ALONE = {
     "latent_one_head": pt.make_config([(L, pt.latent_mixer(heads=1, dim=24, rot_dim=2, vdim=8, kv_rank=30, window=9), None)]),
     "latent_row_of_128": pt.make_config([(L, pt.latent_mixer(heads=5, dim=16, rot_dim=32, vdim=16, kv_rank=96, window=33, scale=0.2), None)]),
     "latent_row_of_64_many_heads": pt.make_config([(L, pt.latent_mixer(heads=18, dim=8, rot_dim=16, vdim=8, kv_rank=48, window=0, scale=0.3), None)]),
+    "latent_row_of_128_window_of_one": pt.make_config([(L, pt.latent_mixer(heads=2, dim=16, rot_dim=32, vdim=16, kv_rank=96, window=1, scale=0.2), None)]),
+    "latent_row_of_64_window_of_two": pt.make_config([(L, pt.latent_mixer(heads=3, dim=16, rot_dim=16, vdim=16, kv_rank=48, window=2, scale=0.2), None)]),
+    "latent_row_of_128_window_of_a_page": pt.make_config([(L, pt.latent_mixer(heads=2, dim=16, rot_dim=64, vdim=16, kv_rank=64, window=64, scale=0.2), None)]),
     "latent_odd_row": pt.make_config([(L, pt.latent_mixer(heads=2, dim=12, rot_dim=6, vdim=10, kv_rank=21, window=13), None)]),
     "dense": pt.make_config([(D, pt.diff_mixer(), pt.dense())]),
     "moe_groups": pt.make_config([(D, pt.diff_mixer(), pt.routed(experts=8, top=3, count=4, keep=2))]),
@@ -165,7 +168,7 @@ ALONE = {
 def test_mechanism_alone(tmp_path, name, dtype):
     cfg = ALONE[name]
     w = write_model(str(tmp_path), cfg, 3)
-    ids = prompt(cfg, 41, 5, w, dtype)
+    ids = prompt(cfg, 141 if "window_of" in name else 41, 5, w, dtype)
     layers = []
     ref = pt.forward(cfg, w, ids, layers)
     eng = engine(str(tmp_path), dtype)
