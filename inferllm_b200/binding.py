@@ -100,7 +100,7 @@ _SIGNATURES = {
     "illm_test_device": [P, PP], "illm_test_device_rewind": [P], "illm_test_device_info": [P, PI, PP, PP],
     "illm_copy_device": [P, P, P, LL], "illm_op_linear": [P, S, P, LL, LL, P, LL, I, I, I, PP, PP, PI],
     "illm_op_linear_gated": [P, S, P, LL, LL, P, LL, I, PP], "illm_policy_gemm_tc_splits": [LL, LL, LL, I],
-    "illm_policy_ring_splits": [LL, I, LL, I, I], "illm_policy_attention_supported": [I, I, I, I, I, I],
+    "illm_policy_ring_splits": [LL, I, LL, I, I], "illm_policy_attention_diff_splits": [LL, I, LL, I], "illm_policy_attention_supported": [I, I, I, I, I, I],
     "illm_policy_attention_kernels": [I, I, I, I, I, PP],
     "illm_register_foreign_part": [S, S, P], "illm_unregister_part": [S, S],
     "illm_sandbox_create": [S, S, I, I, I, LL, P, PP], "illm_sandbox_free": [P], "illm_sandbox_cache": [P], "illm_sandbox_device": [P],

@@ -347,6 +347,9 @@ ILLM_API int illm_policy_gemm_tc_splits(long long M, long long N, long long K, i
 ILLM_API int illm_policy_ring_splits(long long T, int n_kv_heads, long long max_len, int head_dim, int n_sms) {
     return ops::attention_decode_ring_splits(T, n_kv_heads, max_len, head_dim, n_sms);
 }
+ILLM_API int illm_policy_attention_diff_splits(long long T, int head_groups, long long max_seq_len, int n_sms) {
+    return ops::attention_diff_splits(T, head_groups, max_seq_len, n_sms);
+}
 // which: 0 decode_ring, 1 decode (split keys), 2 decode_gqa, 3 prefill (mma.sync), 4 prefill_tc
 ILLM_API int illm_policy_attention_supported(int which, int dtype, int nh, int nkv, int d, int page_size) {
     const DType t = (DType)dtype;

@@ -159,7 +159,7 @@ int illm_latent_attention_any_gated(const void* q, const void* kc, const int* bl
 int illm_latent_rope_prep(const float* x, int ld, int q_off, int H, int d, int dr, int c_off, int R, const float* wkv, float eps, const float* cos_sin, int rot, int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* q_nope, int q_f32, void* qa, void* kc, int act_dtype, int T, int* err, void* stream);
 // stream_ops.cu
 int illm_add_bias(void* y, int dtype, const float* b, int T, int H, void* stream);
-int illm_scaled_add_rmsnorm(float* resid, const float* delta, const float* bias, const float* ls, const float* w, void* y, int act_dtype, int T, int H, float eps, void* stream);
+int illm_scaled_add_rmsnorm(float* resid, const float* delta, const float* ls, const float* w, void* y, int act_dtype, int T, int H, float eps, void* stream);
 
 #ifdef __cplusplus
 }

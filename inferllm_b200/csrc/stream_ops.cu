@@ -146,12 +146,12 @@ extern "C" int illm_add2_rmsnorm(float* resid, const float* d1, const float* d2,
     return illm_launch_status();
 }
 
-// scaled_add_rmsnorm: resid[t, :] += (delta[t, :] (+ bias)) * ls   (a sublayer's output through a per-channel layer scale,
+// scaled_add_rmsnorm: resid[t, :] += delta[t, :] * ls   (a sublayer's output through a per-channel layer scale,
 // all float32), and, if w is given, y[t, :] = resid[t, :] / sqrt(mean(resid^2) + eps) * w in the activation dtype: the
 // layer scale folded into the next norm.  A block per row, the row kept in shared memory between the two passes.
 template <typename TY>
 __global__ void __launch_bounds__(1024)
-scaled_add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta, const float* __restrict__ bias, const float* __restrict__ ls,
+scaled_add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta, const float* __restrict__ ls,
                           const float* __restrict__ w, TY* __restrict__ y, int H, float eps, int vec) {
     pdl_grid_sync();
     extern __shared__ __align__(16) float row_sm[];
@@ -161,15 +161,10 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ d
     if (vec) {          // rows of whole 16-byte pieces: a thread's loads are all in flight before its first store
         const float4* r4 = reinterpret_cast<const float4*>(resid + base);
         const float4* d4 = reinterpret_cast<const float4*>(delta + base);
-        const float4* b4 = bias ? reinterpret_cast<const float4*>(bias) : nullptr;
         const float4* l4 = reinterpret_cast<const float4*>(ls);
         for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
-            float4 v = r4[c], dl = d4[c];
-            const float4 f = l4[c];
-            if (b4) {
-                const float4 bb = b4[c];
-                dl.x += bb.x; dl.y += bb.y; dl.z += bb.z; dl.w += bb.w;
-            }
+            float4 v = r4[c];
+            const float4 dl = d4[c], f = l4[c];
             v.x = fmaf(dl.x, f.x, v.x);
             v.y = fmaf(dl.y, f.y, v.y);
             v.z = fmaf(dl.z, f.z, v.z);
@@ -183,9 +178,7 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ d
         }
     } else {
         for (int c = threadIdx.x; c < H; c += blockDim.x) {
-            float dl = delta[base + c];
-            if (bias) dl += bias[c];
-            const float v = fmaf(dl, ls[c], resid[base + c]);
+            const float v = fmaf(delta[base + c], ls[c], resid[base + c]);
             resid[base + c] = v;
             row_sm[c] = v;
             ss = fmaf(v, v, ss);
@@ -197,7 +190,7 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ d
     for (int c = threadIdx.x; c < H; c += blockDim.x) y[base + c] = from_f32<TY>((row_sm[c] * inv) * w[c]);
 }
 
-extern "C" int illm_scaled_add_rmsnorm(float* resid, const float* delta, const float* bias, const float* ls, const float* w, void* y, int act_dtype,
+extern "C" int illm_scaled_add_rmsnorm(float* resid, const float* delta, const float* ls, const float* w, void* y, int act_dtype,
                                        int T, int H, float eps, void* stream) {
     if (T <= 0 || H <= 0) return 0;
     if (!delta || !ls || (w && !y) || (size_t)H * sizeof(float) > 200 * 1024) return ILLM_ERR_BAD_ARG;
@@ -209,11 +202,11 @@ extern "C" int illm_scaled_add_rmsnorm(float* resid, const float* delta, const f
         cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         raised = true;
     }
-    const int vec = (H & 3) == 0 && !((uintptr_t)resid & 15) && !((uintptr_t)delta & 15) && !((uintptr_t)bias & 15) && !((uintptr_t)ls & 15) ? 1 : 0;
+    const int vec = (H & 3) == 0 && !((uintptr_t)resid & 15) && !((uintptr_t)delta & 15) && !((uintptr_t)ls & 15) ? 1 : 0;
     int threads = ((vec ? H / 4 : H) + 31) / 32 * 32;       // the block size depends on the width alone
     threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
-    if (act_dtype == ILLM_BF16) illm_launch(scaled_add_rmsnorm_kernel<bf16>, dim3(T), dim3(threads), smem, s, resid, delta, bias, ls, w, (bf16*)y, H, eps, vec);
-    else if (act_dtype == ILLM_F32) illm_launch(scaled_add_rmsnorm_kernel<float>, dim3(T), dim3(threads), smem, s, resid, delta, bias, ls, w, (float*)y, H, eps, vec);
+    if (act_dtype == ILLM_BF16) illm_launch(scaled_add_rmsnorm_kernel<bf16>, dim3(T), dim3(threads), smem, s, resid, delta, ls, w, (bf16*)y, H, eps, vec);
+    else if (act_dtype == ILLM_F32) illm_launch(scaled_add_rmsnorm_kernel<float>, dim3(T), dim3(threads), smem, s, resid, delta, ls, w, (float*)y, H, eps, vec);
     else return ILLM_ERR_BAD_ARG;
     return illm_launch_status();
 }

@@ -827,7 +827,7 @@ Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, co
     return y;
 }
 
-Mat scaled_add_rmsnorm(Device& dev, const Mat& resid, const Mat& delta, const float* bias, const float* ls, const Mat* w, float eps, DType out_dtype) {
+Mat scaled_add_rmsnorm(Device& dev, const Mat& resid, const Mat& delta, const float* ls, const Mat* w, float eps, DType out_dtype) {
     need(resid, "resid", true, DType::F32);
     need(delta, "delta", true, DType::F32);
     if (w) need(*w, "norm weight", true, DType::F32);
@@ -837,7 +837,7 @@ Mat scaled_add_rmsnorm(Device& dev, const Mat& resid, const Mat& delta, const fl
     if (resid.cols > kMaxNormWidth) throw KernelError("scaled_add_rmsnorm: width " + std::to_string(resid.cols) + " exceeds what one block's shared memory holds");
     Mat y;
     if (w) y = new_mat(dev, resid.rows, resid.cols, out_dtype);
-    check_kernel(illm_scaled_add_rmsnorm((float*)resid.p, (const float*)delta.p, bias, ls, w ? (const float*)w->p : nullptr, y.p,
+    check_kernel(illm_scaled_add_rmsnorm((float*)resid.p, (const float*)delta.p, ls, w ? (const float*)w->p : nullptr, y.p,
                                          code_of(out_dtype, "scaled_add_rmsnorm"), (int)resid.rows, (int)resid.cols, eps, dev.stream()),
                  "scaled_add_rmsnorm");
     return y;

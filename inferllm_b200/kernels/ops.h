@@ -211,8 +211,8 @@ Mat attention_mixed(Device& dev, const Mat& q, const KVView& kv, const StepView&
 struct DiffAttention {
     float lambda = 0.f, eps = 1e-6f, out_scale = 1.f;
 };
-// Blocks per (token, group of query heads) of a single-token step: as many as fit the GPU at once (two blocks of many heads, or more of few, per SM; a block keeps tens of kilobytes of loads in flight), at most
-// one per 256 keys of the longest sequence the cache allows, at most 64.
+// Blocks per (token, group of query heads) of a single-token step: about two per SM in all (a block keeps tens of
+// kilobytes of loads in flight), at most one per 256 keys of the longest sequence the cache allows, at most 64.
 int attention_diff_splits(long long T, int head_groups, long long max_seq_len, int n_sms);
 Mat attention_diff(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const DiffAttention& p);
 // Attention of the step's tokens over a cache entry: picks the kernel for the dtype, head size and kind of step.
@@ -315,10 +315,10 @@ enum GateAct { kActSilu = 1, kActRelu = 2, kActGeluTanh = 3, kActSwishClamped = 
 int gate_act_from_name(const std::string& name);        // ConfigError-free: -1 for an unknown name
 // resid += d1 (+ d2), all float32 [T, H], and the RMS norm of the new rows times w (float32 [H]) in `out_dtype`: one kernel
 Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, const Mat& weight_f32, float eps, DType out_dtype);
-// resid += (delta (+ bias)) * ls, all float32 (bias, ls float32 [H] on the device; bias may be nullptr), and, with a weight,
+// resid += delta * ls, all float32 (ls float32 [H] on the device), and, with a weight,
 // the RMS norm of the new rows times w (float32 [H]) in `out_dtype`: a sublayer's output through a per-channel layer scale,
 // folded into the next norm.  Without a weight an empty matrix comes back.
-Mat scaled_add_rmsnorm(Device& dev, const Mat& resid, const Mat& delta_f32, const float* bias, const float* ls, const Mat* weight_f32, float eps,
+Mat scaled_add_rmsnorm(Device& dev, const Mat& resid, const Mat& delta_f32, const float* ls, const Mat* weight_f32, float eps,
                        DType out_dtype);
 // y[t, :] += bias (float32 [cols] on the device), in place
 void add_bias(Device& dev, const Mat& y, const float* bias);

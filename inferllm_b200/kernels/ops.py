@@ -436,6 +436,12 @@ def attention_decode_ring_splits(T, n_kv_heads, max_len, head_dim=128, n_sms=Non
     return int(_b.lib().illm_policy_ring_splits(int(T), int(n_kv_heads), int(max_len), int(head_dim), int(n_sms or n_sms_of_device())))
 
 
+def attention_diff_splits(T, head_groups, max_seq_len, n_sms=None) -> int:
+    """Blocks per (token, group of query heads) of the single-token kernel of differential attention: the engine's
+    policy (`ops::attention_diff_splits`), for the SM count of the current device unless given."""
+    return int(_b.lib().illm_policy_attention_diff_splits(int(T), int(head_groups), int(max_seq_len), int(n_sms or n_sms_of_device())))
+
+
 def attention_decode_ring(qkv, k_cache, v_cache, block_table, token_pos, token_seq, n_heads, n_kv_heads,
                           head_dim, page_size, window, scale, max_len, splits=None, rope=None):
     """bfloat16 attention of single tokens as a stream: K/V tiles of 64 keys by TMA through a ring

@@ -231,7 +231,7 @@ struct RMSNorm : Norm {
             const Mat* ls = stream.pending_post->channel_scale();
             if (ls && rows == nullptr && !stream.has_pending2 && !stream.pending.is_partials() && stream.pending.m.dtype == DType::F32 &&
                 weight.m.dtype == DType::F32) {
-                Mat y = ops::scaled_add_rmsnorm(*rt->dev, stream.x, stream.pending.m, nullptr, (const float*)ls->p, &weight.m, eps, rt->dtype);
+                Mat y = ops::scaled_add_rmsnorm(*rt->dev, stream.x, stream.pending.m, (const float*)ls->p, &weight.m, eps, rt->dtype);
                 stream.has_pending = false;
                 stream.pending_post = nullptr;
                 return y;
@@ -271,7 +271,7 @@ struct LayerScale : Norm {
     Mat forward(ResidualStream&, const int*, long long) override { throw EngineError("layer_scale: stands behind a sublayer, not in front of one"); }
     void add_normed_pending(ResidualStream& stream) override {
         Mat y = stream.pending.is_partials() ? ops::materialize(*rt->dev, stream.pending.part, DType::F32) : ops::cast(*rt->dev, stream.pending.m, DType::F32);
-        ops::scaled_add_rmsnorm(*rt->dev, stream.x, y, nullptr, (const float*)factors.m.p, nullptr, 0.f, DType::F32);
+        ops::scaled_add_rmsnorm(*rt->dev, stream.x, y, (const float*)factors.m.p, nullptr, 0.f, DType::F32);
         stream.has_pending = false;
     }
 };

@@ -36,3 +36,16 @@ def test_split_k_of_decode_sized_products():
     assert ops.gemm_tc_splits(65, 4096, 4096) == 1   # larger steps are not split
     assert ops.gemm_tc_splits(8, 22016, 4096) == 1   # 172 tiles fill the GPU by themselves
     assert ops.gemm_tc_splits(8, 4096, 4096) == 8
+
+
+def test_differential_decode_splits():
+    """At most one block per 256 keys of the longest sequence and at most 64; about two blocks per SM in all; one for
+    steps of many tokens; the same for every step of a shape (it looks at the cache's limit, not at the sequences)."""
+    for pairs in (1, 8, 16, 64, 256, 1024, 4096):
+        for longest in (1, 256, 257, 4096, 131072):
+            n = ops.attention_diff_splits(pairs, 1, longest, 148)
+            assert 1 <= n <= min(-(-longest // 256), 64), (pairs, longest, n)
+            assert n == 1 or pairs * n <= 2 * 148
+    assert ops.attention_diff_splits(8, 8, 4096, 148) == 4
+    assert ops.attention_diff_splits(8, 2, 4096, 148) == 16
+    assert ops.attention_diff_splits(512, 8, 4096, 148) == 1
